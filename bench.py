@@ -281,12 +281,14 @@ def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
 
 # ---- another design beside its closest model ---------------------------------------------------
 # the same width, heads, head size, feed-forward and vocabulary (a Vepitar configuration beside the Pugalix one of its width:
-# both mix matrix-state layers with windowed attention)
-DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b", "vepitar-2k": "pugalix-2k", "vepitar-4k": "pugalix-4k"}
+# both mix matrix-state layers with windowed attention; a Kalonex configuration, all attention and gated feed-forwards,
+# beside the Qwen3-shaped one of its width)
+DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b", "vepitar-2k": "pugalix-2k", "vepitar-4k": "pugalix-4k",
+                "kalonex-2k": "1.7b", "kalonex-4k": "8b"}
 OP_CLASSES = ("gemm", "gemm_add", "gemm_swiglu", "gemm_scaled", "gemm_residual", "attention", "attention_decode_rope",
               "qk_norm_rope_kv_write", "state_scan", "head_norm_gate", "gla_decay", "add_rmsnorm", "embed_gather", "swiglu",
               "prenorm_layer_forward", "embed_streams", "delta_scan", "conv_qkv", "attention_sigmoid", "hyper_mix_norm", "moe_route", "moe_act", "moe_rows",
-              "moe_rows_grouped", "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_")
+              "moe_rows_grouped", "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_", "add_bias", "concat_cast", "add_rows", "gemm_w_cols")
 
 
 class OpTimer:
@@ -344,7 +346,7 @@ def design_points(name, layers, steps, warmup, batches, context, torch, ops):
     import numpy as np
     cfg, model = design_model(name, layers, torch)
     vocab = model.spec.vocab
-    out = {"layers": layers, "weights_gb": round(model.weight_bytes_per_step() / 1e9, 3)}
+    out = {"layers": layers, "layer_runs": len(model.spec.schedule), "weights_gb": round(model.weight_bytes_per_step() / 1e9, 3)}
     engine = Engine(model, max_tokens=max(batches) * context, max_slots=max(batches), max_seq_tokens=context)
     fill_cache_random(engine, torch)
     sampler = DeviceSampler(vocab, max(batches), engine.device)

@@ -20,12 +20,15 @@ from typing import Optional, Sequence, Tuple
 @dataclass(frozen=True)
 class RMSNormSpec:
     """y = x * rsqrt(mean(x^2) + eps) * (offset + weight)  (internal/qwen3lm/ops.go:251-254).  The
-    weight is the tensor ``prefix + tensor``; with ``offset`` 1 the checkpoint holds the weight's difference from one."""
+    weight is the tensor ``prefix + tensor``; with ``offset`` 1 the checkpoint holds the weight's difference from one.
+    ``gain`` multiplies the normed row once more (a model that scales its logits by a constant gives that
+    constant to its final norm: the head is linear)."""
     size: int
     eps: float
     kind: str = "rmsnorm"
     tensor: str = "weight"
     offset: float = 0.0
+    gain: float = 1.0     # one more factor on the output, folded into the weight when it is loaded: (offset + weight) * gain
 
 
 @dataclass(frozen=True)
@@ -84,7 +87,14 @@ class GatedAttentionSpec:
     * ``bias``: q, k and v projections carry a bias;
     * ``value_dim``: a value head may have another size than a query/key head;
     * ``window`` > 0 with ``keep_first``: position i sees j <= i if i - j < window or j < keep_first;
-    * ``sink``: the softmax denominator carries one more unit, p_j = exp(s_j) / (1 + sum exp(s));
+    * ``sink``: the softmax denominator carries one more unit, p_j = exp(s_j) / (1 + sum exp(s)); with
+      ``sink_learned`` the unit is exp(z_h) instead, z_h one learned number per head (tensor ``sink``), which
+      is not scaled and has no key and no value;
+    * ``qk_norm`` (an ``RMSNormSpec`` whose eps is used): q and k are RMS-normed after their biases and before the
+      position encoding; with ``qk_norm_span`` over the whole projection at once (all heads of q share one mean of
+      squares and a weight of heads * head_dim, tensor ``q.norm``; k likewise), else head by head with a weight
+      of head_dim;
+    * ``out_bias``: the output projection carries a bias too;
     * ``gate``: the concatenated heads are multiplied by sigmoid of a further projection of the
       mixer's input before the output projection;
     * ``own_kv`` False: the layer has no key/value projections and reads the cache plane of an
@@ -105,7 +115,12 @@ class GatedAttentionSpec:
     bias: bool = False
     gate: bool = False
     own_kv: bool = True
-    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("g", "g"), ("o", "o"))
+    sink_learned: bool = False
+    qk_norm: Optional[RMSNormSpec] = None
+    qk_norm_span: bool = False
+    out_bias: bool = False
+    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("g", "g"), ("o", "o"), ("q_norm", "q.norm"),
+                                          ("k_norm", "k.norm"), ("sink", "sink"))
     bias_suffix: str = ".b"
     kind: str = "gated_attention"
 
@@ -201,13 +216,27 @@ class SigmoidAttentionSpec:
 class MoESpec:
     """Mixture of experts: ``experts`` feed-forwards down(act(up(x))) without biases, act(z) = relu(z)^2,
     of which a token uses ``top``.  Router scores s = softmax(Wr x) over all experts in float32; the
-    ``top`` largest are chosen and weigh their experts' outputs by s / (sum of the chosen s + renorm_eps)."""
+    ``top`` largest are chosen and weigh their experts' outputs by s / (sum of the chosen s + renorm_eps).
+
+    Each of these can be the other way:
+
+    * ``score`` "sigmoid": s = sigmoid(Wr x), every expert's score by itself;
+    * ``renorm`` False: the chosen scores are the weights as they are;
+    * ``weight_on`` "input": a weight multiplies its expert's input, out = sum expert(w x), not its output;
+    * ``act`` "swiglu": an expert is down(silu(gate x) * (up x)) with a third matrix ``e<j>.gate``;
+    * ``shared``: a ``SwiGLUSpec`` of a further expert under ``shared_prefix`` that every token uses, with weight 1."""
     hidden: int
     experts: int
     top: int
     intermediate: int
     renorm_eps: float = 1e-20
     kind: str = "moe"
+    score: str = "softmax"
+    renorm: bool = True
+    weight_on: str = "output"
+    act: str = "relu2"
+    shared: Optional[object] = None
+    shared_prefix: str = "shared."
 
 
 @dataclass(frozen=True)
@@ -271,16 +300,35 @@ class HyperLayerSpec:
 
 
 @dataclass(frozen=True)
+class ReinjectSpec:
+    """What happens to the residual where a pass through repeated layers begins: with the embedding output x0,
+
+        x <- W [x; x0] + steps[index]
+
+    W: the tensor ``weight`` ([hidden, 2 hidden], the residual's columns first); ``steps``: a tensor
+    [passes, hidden] of one vector per pass.  The product's inputs are in the activation dtype, its sums and the
+    new residual float32."""
+    hidden: int
+    passes: int
+    index: int
+    weight: str = "loop.in"
+    steps: str = "loop.step"
+    kind: str = "reinject"
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer.
 
     ``layer`` indexes ``ModelSpec.layers``; a layer may appear in several entries (its weights are
     then used more than once, each run with a cache plane of its own).  ``cache_of`` names the
     schedule position whose cache plane this run reads instead of writing one of its own
-    (None: own plane).
+    (None: own plane).  ``enter``: the spec of a *junction* part (registry category ``junction``) that
+    rewrites the residual right before this run (``ReinjectSpec``), or None.
     """
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[object] = None
 
 
 @dataclass(frozen=True)

@@ -41,7 +41,8 @@ struct AttnParams {
 struct AttnParamsX : AttnParams {
     int dv;          // size of a value head; 0: the same as d.  Only the CUDA-core kernel takes another size.
     int keep_first;  // with a window: keys at positions below this stay visible however far back they lie
-    int sink;        // 1: the softmax denominator carries one more unit (a key of score 0 without a value)
+    int sink;        // 1: the softmax denominator carries one more term (a key without a value): exp(sinks[head]), or one unit
+    const float* sinks;  // [heads] the sink's score per head, in the units of the scaled scores but not scaled itself; null: 0
 };
 
 // Per-head q/k RMSNorm, rotary embedding and cache write on the rows of a fused q|k|v buffer.
@@ -75,6 +76,7 @@ struct QkRopeParamsX : QkRopeParams {
     const float* v_b;
     int pairs;         // 1: channels 2j and 2j + 1 turn together by angle j; 0: channels j and j + rot / 2
     int dv;            // size of a value head; 0: the same as d
+    int span;          // 1: q is normed over all its heads together (q_w: [heads * d]) and k likewise (k_w: [kv_heads * d]); 0: per head
 };
 
 // A matrix state per (sequence, head), updated token by token: S <- diag(a) S + b k v^T, o = S^T q.
@@ -129,6 +131,8 @@ GB_API int gb_add_rmsnorm(float* h, const float* delta, const float* w, float ep
 GB_API int gb_swiglu(const void* gu, void* out, int dtype, int rows, int inter, int interleave8, cudaStream_t stream);
 GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* p, int dtype, cudaStream_t stream);
 GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* p, int dtype, cudaStream_t stream);
+GB_API int gb_add_bias(float* out, const float* bias, int rows, int n, cudaStream_t stream);
+GB_API int gb_concat_cast(const float* h, const float* delta, const float* side, void* out, int out_dtype, int rows, int n, cudaStream_t stream);
 
 // matrix products: C[M, N] = A[M, K] W[N, K]^T
 GB_API int gb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int M, int N, int K, int64_t lda,
@@ -170,6 +174,7 @@ static inline AttnParamsX gb_attn_widen(const AttnParams& a) {
     AttnParamsX x;
     static_cast<AttnParams&>(x) = a;
     x.dv = x.keep_first = x.sink = 0;
+    x.sinks = nullptr;
     return x;
 }
 
@@ -274,6 +279,8 @@ struct MoeRouteParams {
     float* dense;           // [rows, experts]: the weight of every expert, 0 where not chosen
     int* index;             // [rows, top]
     float* weight;          // [rows, top]
+    int score_kind;         // 0: softmax over all experts; 1: sigmoid of each logit by itself
+    int renorm;             // 1: the chosen scores are divided by their sum + renorm_eps; 0: they are the weights
 };
 GB_API int gb_moe_route(const MoeRouteParams* p, cudaStream_t stream);
 GB_API int gb_moe_act(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
@@ -289,8 +296,14 @@ struct MoeRowsParams {
     const int* index;
     const float* weight;
     int rows, experts, top, ff, hidden;
+    int act_kind;           // 0: relu(up x)^2; 1: gated, silu(gate x) * (up x), `up` holding each expert's gate rows, then its up rows
+    int weight_input;       // 1: a pair's weight multiplies its expert's input; 0: its output
 };
+GB_API int gb_moe_act_kind(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
+                           int kind, int weight_input, int dtype, cudaStream_t stream);
 GB_API int gb_moe_rows(const MoeRowsParams* p, int dtype, int w_dtype, cudaStream_t stream);
+GB_API int gb_moe_group_weights(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, const float* weight,
+                                float* sorted_weight, cudaStream_t stream);
 GB_API int gb_moe_group(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, cudaStream_t stream);
 GB_API int gb_moe_gather(const void* x, int64_t x_stride, const int* src_row, void* xs, int pairs, int hidden, int dtype, cudaStream_t stream);
 GB_API int gb_relu2(void* z, int64_t n, int dtype, cudaStream_t stream);

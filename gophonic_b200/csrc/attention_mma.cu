@@ -20,7 +20,7 @@
 
 
 int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
-                              int nseq, int heads, int d, int num_splits, int sink, cudaStream_t stream);
+                              int nseq, int heads, int d, int num_splits, int sink, const float* sinks, cudaStream_t stream);
 
 namespace {
 
@@ -199,10 +199,11 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParamsX p) {
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     if (p.sink) {
         // one more unit in the denominator: a key of score 0 that has no value
-        const float f0 = fmaxf(m0, 0.f), f1 = fmaxf(m1, 0.f);
+        const float z = p.sinks ? p.sinks[head] * LOG2E : 0.f;   // the head's own score for it, in the sums' base-2 units
+        const float f0 = fmaxf(m0, z), f1 = fmaxf(m1, z);
         const float k0 = exp2f(m0 - f0), k1 = exp2f(m1 - f1);
-        l0 = l0 * k0 + exp2f(-f0);
-        l1 = l1 * k1 + exp2f(-f1);
+        l0 = l0 * k0 + exp2f(z - f0);
+        l1 = l1 * k1 + exp2f(z - f1);
 #pragma unroll
         for (int j = 0; j < NF; j++) {
             o[j][0] *= k0;
@@ -554,8 +555,9 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParamsX p, Rop
         float L = 0.f, acc = 0.f;
         const bool sink_here = p.sink && p.num_splits == 1;   // with key splits the merge kernel adds the sink's unit
         if (sink_here) {
-            M = fmaxf(M, 0.f);
-            L = exp2f(-M);
+            const float z = p.sinks ? p.sinks[h0 + r] * LOG2E : 0.f;
+            M = fmaxf(M, z);
+            L = exp2f(z - M);
         }
         if (M != -INFINITY) {
 #pragma unroll
@@ -626,7 +628,7 @@ int launch_decode(const AttnParamsX& p, const RopeFuse& f, cudaStream_t stream) 
     GB_CHECK_LAUNCH("attention_decode_mma");
     if (p.num_splits > 1)
         return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, p.d,
-                                         p.num_splits, p.sink, stream);
+                                         p.num_splits, p.sink, p.sinks, stream);
     return 0;
 }
 

@@ -167,10 +167,11 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
             T* op = (T*)p.out + (int64_t)(q_start + row_q[rr]) * p.out_row_stride + (int64_t)row_head[rr] * dv;
             float lsum = l[rr], keep = 1.f;
             if (p.sink) {
-                // one more unit in the denominator: a key of score 0 that has no value
-                const float mf = fmaxf(m[rr], 0.f);
+                // one more term in the denominator: a key that has no value, of score 0 or the head's own
+                const float z = p.sinks ? p.sinks[row_head[rr]] : 0.f;
+                const float mf = fmaxf(m[rr], z);
                 keep = expf(m[rr] - mf);
-                lsum = lsum * keep + expf(-mf);
+                lsum = lsum * keep + expf(z - mf);
             }
             float inv = keep / lsum;
 #pragma unroll
@@ -201,7 +202,8 @@ constexpr int MERGE_MAX_SPLITS = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int64_t out_row_stride,
-                                                         const int* __restrict__ seq_q_start, int heads, int d, int num_splits, int sink) {
+                                                         const int* __restrict__ seq_q_start, int heads, int d, int num_splits, int sink,
+                                                         const float* __restrict__ sinks) {
     __shared__ float w_s[MERGE_MAX_SPLITS];
     __shared__ float l_s;
     pdl_trigger();  // the product that follows may start fetching its weights
@@ -212,7 +214,8 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
         float M = -INFINITY;
         for (int s = lane; s < num_splits; s += 32) M = fmaxf(M, sp[(int64_t)s * (d + 2)]);
         M = warp_max(M);
-        if (sink) M = fmaxf(M, 0.f);  // the sink's score
+        const float z = sinks ? sinks[head] : 0.f;  // the sink's score
+        if (sink) M = fmaxf(M, z);
         float L = 0.f;
         for (int s = lane; s < num_splits; s += 32) {
             const float ms = sp[(int64_t)s * (d + 2)];
@@ -221,7 +224,7 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const float* __restrict
             L += w * sp[(int64_t)s * (d + 2) + 1];
         }
         L = warp_sum(L);
-        if (sink) L += expf(-M);
+        if (sink) L += expf(z - M);
         if (lane == 0) l_s = L;
     }
     __syncthreads();
@@ -282,7 +285,7 @@ int launch(const AttnParamsX& p, cudaStream_t stream) {
     if (rc) return rc;
     if (p.num_splits > 1) {
         attn_merge_kernel<T><<<dim3(p.heads, p.nseq), 128, 0, stream>>>(p.scratch, (T*)p.out, p.out_row_stride,
-                                                                        p.seq_q_start, p.heads, dv, p.num_splits, p.sink);
+                                                                        p.seq_q_start, p.heads, dv, p.num_splits, p.sink, p.sinks);
         GB_CHECK_LAUNCH("attention_merge");
     }
     return 0;
@@ -292,13 +295,13 @@ int launch(const AttnParamsX& p, cudaStream_t stream) {
 
 // Merge of per-split partial results, shared with the tensor-core single-token kernel.
 int gb_attention_merge_launch(const float* scratch, void* out, int dtype, int64_t out_row_stride, const int* seq_q_start,
-                              int nseq, int heads, int d, int num_splits, int sink, cudaStream_t stream) {
+                              int nseq, int heads, int d, int num_splits, int sink, const float* sinks, cudaStream_t stream) {
     if (num_splits > MERGE_MAX_SPLITS) GB_REFUSE("attention: %d key splits; at most %d", num_splits, MERGE_MAX_SPLITS);
     if (dtype == GB_F32)
-        attn_merge_kernel<float><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (float*)out, out_row_stride, seq_q_start, heads, d, num_splits, sink);
+        attn_merge_kernel<float><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (float*)out, out_row_stride, seq_q_start, heads, d, num_splits, sink, sinks);
     else
         attn_merge_kernel<__nv_bfloat16><<<dim3(heads, nseq), 128, 0, stream>>>(scratch, (__nv_bfloat16*)out, out_row_stride,
-                                                                                seq_q_start, heads, d, num_splits, sink);
+                                                                                seq_q_start, heads, d, num_splits, sink, sinks);
     GB_CHECK_LAUNCH("attention_merge");
     return 0;
 }

@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             // a sink adds one unit to the denominator: a key of score 0, in the scale the sums are kept in
             // (a sum so scaled that the unit overflows gives 1 / inf = 0, which is the limit)
-            if (!sig && p.sink && m_used != -INFINITY) l += exp2f(-m_used);
+            if (!sig && p.sink && m_used != -INFINITY) l += exp2f((p.sinks ? p.sinks[head] * LOG2E : 0.f) - m_used);
             float inv = 1.f / l;
             if (sig) {
                 inv = 1.f;

@@ -425,6 +425,96 @@ __global__ void qk_rope_kernel(QkRopeParamsX p) {
     }
 }
 
+// The same work where the norm runs over a whole projection: all heads of q share one sum of squares and one
+// weight vector [heads * d], all heads of k likewise.  One CTA a row: the biased q and k of the row are staged
+// in shared memory as float32 while their squares are added up (a lane's share in element order, lanes by a
+// shuffle tree, warps in warp order: the same order whatever else the step holds), then every element is
+// normed with its partner, rotated and stored (q in place, k and v at the row's position in the cache).
+template <typename T>
+__global__ void __launch_bounds__(256) qk_rope_span_kernel(QkRopeParamsX p) {
+    extern __shared__ float sh[];  // [heads * d + kv_heads * d] values, then [2][8] partial sums
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = blockIdx.x;
+    const int d = p.d, dv = p.dv > 0 ? p.dv : d;
+    const int nq = p.heads * d, nk = p.kv_heads * d, nv = p.kv_heads * dv;
+    float* y = sh;
+    float* part = sh + nq + nk;
+    T* row = (T*)p.qkv + (int64_t)r * p.row_stride;
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < nq; i += 256) {
+        float v = to_f32<T>(row[i]);
+        if (p.q_b) v += p.q_b[i];
+        y[i] = v;
+        sq += v * v;
+    }
+    for (int i = tid; i < nk; i += 256) {
+        float v = to_f32<T>(row[nq + i]);
+        if (p.k_b) v += p.k_b[i];
+        y[nq + i] = v;
+        sk += v * v;
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) part[warp] = sq, part[8 + warp] = sk;
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tq += part[w], tk += part[8 + w];
+    const float inv_q = p.q_w ? 1.0f / sqrtf(tq / (float)nq + p.eps) : 1.f;
+    const float inv_k = p.k_w && nk > 0 ? 1.0f / sqrtf(tk / (float)nk + p.eps) : 1.f;
+    const int pos = p.row_pos[r];
+    const int half = p.rot / 2;
+    const int tpos = (half == 0 || gb_check(pos, p.table_positions, GB_CHECK_ROPE_POSITION)) ? pos : 0;
+    const float* c = p.cos_t + (int64_t)tpos * half;
+    const float* s = p.sin_t + (int64_t)tpos * half;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (p.write_kv && p.kv_heads > 0) {
+        const int slot = p.seq_slot[p.row_seq[r]];
+        const int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot, p.max_slots), pos, p.bt_stride, p.pages);
+        kdst = (T*)p.k_plane + (page * p.kv_heads * GB_PAGE + (pos % GB_PAGE)) * (int64_t)d;
+        vdst = (T*)p.v_plane + (page * p.kv_heads * GB_PAGE + (pos % GB_PAGE)) * (int64_t)dv;
+    }
+    const int n_rot = nq + (kdst ? nk : 0);
+    for (int i = tid; i < n_rot; i += 256) {
+        const bool is_q = i < nq;
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = is_q ? p.q_w : p.k_w;
+        const int base = is_q ? 0 : nq;          // where this projection's weights and heads start
+        const int e = (i - base) % d;
+        auto normed = [&](int at) { return w ? y[at] * inv * w[at - base] : y[at]; };
+        float v;
+        if (p.pairs) {
+            if (e < p.rot) {
+                const int j = e >> 1;
+                v = (e & 1) ? normed(i) * c[j] + normed(i - 1) * s[j] : normed(i) * c[j] - normed(i + 1) * s[j];
+            } else {
+                v = normed(i);
+            }
+        } else if (e < half)
+            v = normed(i) * c[e] - normed(i + half) * s[e];
+        else if (e < p.rot)
+            v = normed(i) * c[e - half] + normed(i - half) * s[e - half];
+        else
+            v = normed(i);
+        if (is_q) {
+            row[i] = from_f32<T>(v);
+        } else {
+            const int kvh = (i - nq) / d;
+            kdst[(int64_t)kvh * GB_PAGE * d + e] = from_f32<T>(v);
+        }
+    }
+    if (vdst) {
+        const T* vsrc = row + nq + nk;
+        for (int i = tid; i < nv; i += 256) {
+            const int kvh = i / dv, e = i - kvh * dv;
+            float v = to_f32<T>(vsrc[i]);
+            if (p.v_b) v += p.v_b[i];
+            vdst[(int64_t)kvh * GB_PAGE * dv + e] = from_f32<T>(v);
+        }
+    }
+}
+
 // The common geometry (bfloat16, head_dim 128 rotated in full): a warp per head and ROPE_ROWS
 // consecutive rows, every lane holds four consecutive elements of each row, so element i and its
 // partner i + 64 sit in lanes l and l ^ 16.  All loads of the warp's rows (positions, elements,
@@ -613,7 +703,7 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     QkRopeParamsX x;
     static_cast<QkRopeParams&>(x) = *pp;
     x.q_b = x.k_b = x.v_b = nullptr;
-    x.pairs = x.dv = 0;
+    x.pairs = x.dv = x.span = 0;
     return gb_qk_norm_rope_kv_write_x(&x, dtype, stream);
 }
 
@@ -627,6 +717,21 @@ GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* pp, int dtype, cudaSt
     if (p.rows > 0x7fffffff / 2) GB_REFUSE("qk_norm_rope: %d rows are too many", p.rows);
     int total_heads = p.heads + 2 * p.kv_heads;
     if (p.dv < 0 || p.dv > 1024) GB_REFUSE("qk_norm_rope: value size %d is outside [1, 1024]", p.dv);
+    if (p.span) {
+        const size_t span_smem = ((size_t)(p.heads + p.kv_heads) * p.d + 16) * sizeof(float);
+        if (span_smem > 200 * 1024) GB_REFUSE("qk_norm_rope: %d + %d heads of %d exceed what one CTA stages", p.heads, p.kv_heads, p.d);
+        if (dtype != GB_F32 && dtype != GB_BF16) GB_REFUSE("qk_norm_rope: unknown dtype %d", dtype);
+        if (dtype == GB_F32) {
+            if (span_smem > 48 * 1024) cudaFuncSetAttribute(qk_rope_span_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem);
+            qk_rope_span_kernel<float><<<p.rows, 256, span_smem, stream>>>(p);
+        } else {
+            if (span_smem > 48 * 1024)
+                cudaFuncSetAttribute(qk_rope_span_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem);
+            qk_rope_span_kernel<__nv_bfloat16><<<p.rows, 256, span_smem, stream>>>(p);
+        }
+        GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
+        return 0;
+    }
     const bool plain = !p.q_b && !p.k_b && !p.v_b && !p.pairs && (p.dv == 0 || p.dv == p.d);
     if (plain && dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
         !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
@@ -652,6 +757,58 @@ GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* pp, int dtype, cudaSt
     else
         GB_REFUSE("qk_norm_rope: unknown dtype %d", dtype);
     GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// out[r, :] += bias, float32: the bias of a projection whose product left float32 rows
+__global__ void add_bias_kernel(float* __restrict__ out, const float* __restrict__ bias, int n, int64_t total) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] += bias[i % n];
+}
+
+GB_API int gb_add_bias(float* out, const float* bias, int rows, int n, cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return 0;
+    const int64_t total = (int64_t)rows * n;
+    const int64_t blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffff) GB_REFUSE("add_bias: %d x %d elements are too many", rows, n);
+    add_bias_kernel<<<(unsigned)blocks, 256, 0, stream>>>(out, bias, n, total);
+    GB_CHECK_LAUNCH("add_bias");
+    return 0;
+}
+
+// out[r, :n] = h[r] (+ delta[r]), out[r, n:] = side[r], in the activation dtype: the residual and a second stream of
+// float32 rows laid side by side as the input of one product.  h itself is left as it is.
+template <typename TO>
+__global__ void concat_cast_kernel(const float* __restrict__ h, const float* __restrict__ delta, const float* __restrict__ side,
+                                   TO* __restrict__ out, int n, int64_t total) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int64_t r = i / (2 * n);
+    const int c = (int)(i - r * 2 * n);
+    float v;
+    if (c < n) {
+        v = h[r * n + c];
+        if (delta) v += delta[r * n + c];
+    } else {
+        v = side[r * n + c - n];
+    }
+    out[i] = from_f32<TO>(v);
+}
+
+GB_API int gb_concat_cast(const float* h, const float* delta, const float* side, void* out, int out_dtype, int rows, int n,
+                          cudaStream_t stream) {
+    if (rows <= 0 || n <= 0) return 0;
+    const int64_t total = (int64_t)rows * 2 * n;
+    const int64_t blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffff) GB_REFUSE("concat_cast: %d x %d elements are too many", rows, 2 * n);
+    if (out_dtype == GB_F32)
+        concat_cast_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(h, delta, side, (float*)out, n, total);
+    else if (out_dtype == GB_BF16)
+        concat_cast_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(h, delta, side, (__nv_bfloat16*)out, n, total);
+    else
+        GB_REFUSE("concat_cast: unknown dtype %d", out_dtype);
+    GB_CHECK_LAUNCH("concat_cast");
     return 0;
 }
 

@@ -47,11 +47,12 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
 #pragma unroll
     for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++) {
         const int i = lane + 32 * e;
-        s[e] = i < E ? expf(s[e] - mx) : -1.f;     // scores are positive; -1 marks what is absent or taken
+        // scores are not negative; -1 marks what is absent or taken
+        s[e] = i < E ? (p.score_kind == 1 ? 1.f / (1.f + expf(-s[e])) : expf(s[e] - mx)) : -1.f;
         if (i < E) sum += s[e];
     }
     sum = warp_sum(sum);
-    const float inv = 1.f / sum;
+    const float inv = p.score_kind == 1 ? 1.f : 1.f / sum;     // a sigmoid score stands by itself
     float* dense = p.dense + row * E;
     for (int i = lane; i < E; i += 32) dense[i] = 0.f;
     float chosen_sum = 0.f;
@@ -79,7 +80,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
         if (lane == (k & 31)) my_w = sc, my_i = best_i;
         if (k >= 32 && lane == 0) {}   // more than 32 choices are refused on the host
     }
-    const float norm = 1.f / (chosen_sum + p.renorm_eps);
+    const float norm = p.renorm ? 1.f / (chosen_sum + p.renorm_eps) : 1.f;
     __syncwarp();
     if (lane < p.top) {
         const float w = my_w * norm;
@@ -89,16 +90,39 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
     }
 }
 
+// What an expert's hidden unit makes of its product(s) z (and, for a gated expert, u) and the pair's weight w:
+// kind 0: relu(z)^2; kind 1: silu(z) * u.  The weight multiplies the result, or (weight_input) the expert's
+// input, which for products without biases is the same as multiplying z and u.
+__device__ __forceinline__ float expert_act(float z, float u, float w, int kind, int weight_input) {
+    if (weight_input) z *= w, u *= w;
+    float a;
+    if (kind == 1) {
+        a = z / (1.f + expf(-z)) * u;
+    } else {
+        const float r = fmaxf(z, 0.f);
+        a = r * r;
+    }
+    return weight_input ? a : w * a;
+}
+
+// up: [rows, experts * (kind 1: 2 ff, gate rows then up rows of each expert; else ff)]; dense null: every weight is 1
 template <typename T>
 __global__ void moe_act_kernel(const T* __restrict__ up, int64_t up_stride, const float* __restrict__ dense, T* __restrict__ act,
-                               int64_t act_stride, int rows, int experts, int ff) {
+                               int64_t act_stride, int rows, int experts, int ff, int kind, int weight_input) {
     const int64_t n = (int64_t)experts * ff;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * n) return;
     const int64_t r = idx / n, c = idx % n;
-    const float w = dense[r * experts + c / ff];
-    const float z = fmaxf(to_f32<T>(up[r * up_stride + c]), 0.f);
-    act[r * act_stride + c] = from_f32<T>(w * z * z);
+    const int64_t e = c / ff, i = c - e * ff;
+    const float w = dense ? dense[r * experts + e] : 1.f;
+    float z, u = 0.f;
+    if (kind == 1) {
+        z = to_f32<T>(up[r * up_stride + e * 2 * ff + i]);
+        u = to_f32<T>(up[r * up_stride + e * 2 * ff + ff + i]);
+    } else {
+        z = to_f32<T>(up[r * up_stride + c]);
+    }
+    act[r * act_stride + c] = from_f32<T>(expert_act(z, u, w, kind, weight_input));
 }
 
 // a warp's share of the dot product of a weight row and a row of activations, 16 bytes a lane where both allow it
@@ -138,13 +162,15 @@ __global__ void __launch_bounds__(128) moe_up_rows_kernel(MoeRowsParams p) {
     if (i >= p.ff) return;
     const int r = pair / p.top;
     const int e = p.index[pair];
-    const TW* w = (const TW*)p.up + ((int64_t)e * p.ff + i) * p.hidden;
+    const int per = p.act_kind == 1 ? 2 : 1;      // a gated expert holds its gate rows, then its up rows
+    const TW* w = (const TW*)p.up + ((int64_t)e * per * p.ff + i) * p.hidden;
     const T* x = (const T*)p.x + (int64_t)r * p.x_stride;
     const float a = warp_sum(warp_dot<T, TW>(w, x, p.hidden, lane));
+    const float b = p.act_kind == 1 ? warp_sum(warp_dot<T, TW>(w + (int64_t)p.ff * p.hidden, x, p.hidden, lane)) : 0.f;
     if (lane == 0) {
         // the same roundings as the stacked path: the product in the activation dtype, then the activation
-        const float z = fmaxf(to_f32<T>(from_f32<T>(a)), 0.f);
-        ((T*)p.act)[(int64_t)pair * p.ff + i] = from_f32<T>(p.weight[pair] * z * z);
+        ((T*)p.act)[(int64_t)pair * p.ff + i] =
+            from_f32<T>(expert_act(to_f32<T>(from_f32<T>(a)), to_f32<T>(from_f32<T>(b)), p.weight[pair], p.act_kind, p.weight_input));
     }
 }
 
@@ -176,13 +202,18 @@ __global__ void __launch_bounds__(128) moe_up_grouped_kernel(MoeRowsParams p, co
     const int i = blockIdx.x * 4 + warp, e = blockIdx.y;
     const int lo = offsets[e], hi = offsets[e + 1];
     if (i >= p.ff || lo == hi) return;
-    const TW* w = (const TW*)p.up + ((int64_t)e * p.ff + i) * p.hidden;
+    const int per = p.act_kind == 1 ? 2 : 1;
+    const TW* w = (const TW*)p.up + ((int64_t)e * per * p.ff + i) * p.hidden;
     for (int at = lo; at < hi; at++) {
         const T* x = (const T*)p.x + (int64_t)src_row[at] * p.x_stride;
         const float a = warp_sum(warp_dot<T, TW>(w, x, p.hidden, lane));
+        const float b = p.act_kind == 1 ? warp_sum(warp_dot<T, TW>(w + (int64_t)p.ff * p.hidden, x, p.hidden, lane)) : 0.f;
         if (lane == 0) {
-            const float z = fmaxf(to_f32<T>(from_f32<T>(a)), 0.f);
-            ((T*)p.act)[(int64_t)at * p.ff + i] = from_f32<T>(z * z);
+            // a weight on the expert's input is applied here (p.weight: the pairs' weights in sorted order), one on its
+            // output when the rows are added up
+            const float pw = p.weight_input ? p.weight[at] : 1.f;
+            ((T*)p.act)[(int64_t)at * p.ff + i] =
+                from_f32<T>(expert_act(to_f32<T>(from_f32<T>(a)), to_f32<T>(from_f32<T>(b)), pw, p.act_kind, p.weight_input));
         }
     }
 }
@@ -205,7 +236,8 @@ constexpr int GROUP_MAX_EXPERTS = 512;
 
 // one CTA: counts of the pairs of each expert, offsets of the experts' groups, and a place in its group for every pair
 __global__ void __launch_bounds__(GROUP_THREADS) moe_group_kernel(const int* __restrict__ index, int pairs, int top, int experts,
-                                                                 int* __restrict__ offsets, int* __restrict__ place, int* __restrict__ src_row) {
+                                                                 int* __restrict__ offsets, int* __restrict__ place, int* __restrict__ src_row,
+                                                                 const float* __restrict__ weight, float* __restrict__ sorted_weight) {
     __shared__ int count[GROUP_MAX_EXPERTS], cursor[GROUP_MAX_EXPERTS];
     const int tid = threadIdx.x;
     for (int e = tid; e < experts; e += GROUP_THREADS) count[e] = 0;
@@ -226,6 +258,7 @@ __global__ void __launch_bounds__(GROUP_THREADS) moe_group_kernel(const int* __r
         const int at = atomicAdd(&cursor[index[i]], 1);
         place[i] = at;
         src_row[at] = i / top;
+        if (sorted_weight) sorted_weight[at] = weight[i];
     }
 }
 
@@ -258,7 +291,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __re
     const int64_t r = blockIdx.x;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float a = 0.f;
-        for (int k = 0; k < top; k++) a = fmaf(weight[r * top + k], ys[(int64_t)place[r * top + k] * hidden + c], a);
+        for (int k = 0; k < top; k++) a = fmaf(weight ? weight[r * top + k] : 1.f, ys[(int64_t)place[r * top + k] * hidden + c], a);
         out[r * out_stride + c] = a;
     }
 }
@@ -266,9 +299,16 @@ __global__ void moe_combine_kernel(const float* __restrict__ ys, const int* __re
 }  // namespace
 
 GB_API int gb_moe_group(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, cudaStream_t stream) {
+    return gb_moe_group_weights(index, rows, top, experts, offsets, place, src_row, nullptr, nullptr, stream);
+}
+
+// The same, and the pairs' weights in sorted order beside them (sorted_weight[place[i]] = weight[i]) if both are given.
+GB_API int gb_moe_group_weights(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, const float* weight,
+                                float* sorted_weight, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (experts <= 0 || experts > GROUP_MAX_EXPERTS || top <= 0) GB_REFUSE("moe_group: %d experts, %d a token", experts, top);
-    moe_group_kernel<<<1, GROUP_THREADS, 0, stream>>>(index, rows * top, top, experts, offsets, place, src_row);
+    if ((weight != nullptr) != (sorted_weight != nullptr)) GB_REFUSE("moe_group: weights in and out go together");
+    moe_group_kernel<<<1, GROUP_THREADS, 0, stream>>>(index, rows * top, top, experts, offsets, place, src_row, weight, sorted_weight);
     GB_CHECK_LAUNCH("moe_group");
     return 0;
 }
@@ -319,15 +359,23 @@ GB_API int gb_moe_route(const MoeRouteParams* pp, cudaStream_t stream) {
 
 GB_API int gb_moe_act(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
                       int dtype, cudaStream_t stream) {
+    return gb_moe_act_kind(up, up_stride, dense, act, act_stride, rows, experts, ff, 0, 0, dtype, stream);
+}
+
+// kind 0: weight * relu(up)^2; kind 1: gated, silu(gate) * up with each expert's gate columns ahead of its up columns.
+// weight_input 1: the weight multiplies the expert's input instead of its output.  dense null: weights of 1.
+GB_API int gb_moe_act_kind(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
+                           int kind, int weight_input, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (experts <= 0 || ff <= 0) GB_REFUSE("moe_act: %d experts of %d", experts, ff);
+    if (kind != 0 && kind != 1) GB_REFUSE("moe_act: unknown activation %d", kind);
     const int64_t total = (int64_t)rows * experts * ff;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == GB_F32)
-        moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)up, up_stride, dense, (float*)act, act_stride, rows, experts, ff);
+        moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)up, up_stride, dense, (float*)act, act_stride, rows, experts, ff, kind, weight_input);
     else if (dtype == GB_BF16)
         moe_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)up, up_stride, dense, (__nv_bfloat16*)act, act_stride,
-                                                                  rows, experts, ff);
+                                                                  rows, experts, ff, kind, weight_input);
     else
         GB_REFUSE("moe_act: unknown dtype %d", dtype);
     GB_CHECK_LAUNCH("moe_act");
@@ -361,7 +409,7 @@ GB_API int gb_moe_rows_grouped(const MoeRowsParams* pp, const int* offsets, cons
     MoeRowsParams p = *pp;
     if (p.rows <= 0) return 0;
     if (p.experts <= 0 || p.experts > 65535 || p.top <= 0 || p.ff <= 0 || p.hidden <= 0) GB_REFUSE("moe_rows: %d experts, %d a token, %d x %d", p.experts, p.top, p.ff, p.hidden);
-    if (!p.x || !p.up || !p.down || !p.act || !offsets || !src_row || !ys) GB_REFUSE("moe_rows: a tensor is missing");
+    if (!p.x || !p.up || !p.down || !p.act || !offsets || !src_row || !ys || (p.weight_input && !p.weight)) GB_REFUSE("moe_rows: a tensor is missing");
     dim3 ugrid((p.ff + 3) / 4, p.experts), dgrid((p.hidden + 3) / 4, p.experts);
     if (dtype == GB_BF16 && w_dtype == GB_BF16) {
         moe_up_grouped_kernel<__nv_bfloat16, __nv_bfloat16><<<ugrid, 128, 0, stream>>>(p, offsets, src_row);

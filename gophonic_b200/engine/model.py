@@ -58,6 +58,11 @@ class Model:
         self.streams = int(getattr(spec, "streams", 1))
         if any(self._takes_streams) != all(self._takes_streams) or (self.streams > 1 and not all(self._takes_streams)):
             raise ValueError("model spec: a residual kept in streams needs blocks that take streams, all of them")
+        # junctions: parts that rewrite the residual right before a run of the schedule
+        self.junctions = {pos: registry.part_class("junction", e.enter.kind)(e.enter, "", tensors, runtime)
+                          for pos, e in enumerate(spec.schedule) if getattr(e, "enter", None) is not None}
+        if self.junctions and self._takes_streams[0]:
+            raise ValueError("model spec: a junction rewrites one residual; blocks that keep it in streams cannot have one")
         # a block arrangement may take the norm that follows it (to prepare the residual's rows for it)
         self._takes_next_norm = ["next_norm" in inspect.signature(b.forward).parameters for b in self.blocks]
         norm_prefix = final_norm_prefix(spec)
@@ -126,13 +131,14 @@ class Model:
     @property
     def capturable(self) -> bool:
         """Whether every part only enqueues stream work, so a step can be captured in a CUDA graph."""
-        return all(b.capturable for b in self.blocks) and self.final_norm.capturable
+        return all(b.capturable for b in self.blocks) and self.final_norm.capturable and all(j.capturable for j in self.junctions.values())
 
     def weight_bytes_per_step(self) -> int:
         """Bytes of weights a step reads once: every layer run's matrices and the head."""
         total = self.head.numel() * self.head.element_size()
         for entry in self.spec.schedule:
             total += self.blocks[entry.layer].weight_bytes()
+        total += sum(j.weight_bytes() for j in self.junctions.values() if hasattr(j, "weight_bytes"))
         return total
 
     # ---- forward -------------------------------------------------------------------------
@@ -163,11 +169,21 @@ class Model:
             pending = RowStats(stats, 1, prescaled[:rows], first.first_norm())
         else:
             ops.embed_gather(self.embedding, batch.ids, h, scale=scale)
+        x0 = None
+        if self.junctions:
+            # a junction reads the embedding output again; blocks change the residual in place, so it is kept apart
+            # (unless a junction is the first thing that happens: it leaves its input as it is)
+            x0 = h
+            if 0 not in self.junctions:
+                x0 = torch.empty_like(h)
+                ops.embed_gather(self.embedding, batch.ids, x0, scale=scale)
         for pos, entry in enumerate(schedule):
             block = self.blocks[entry.layer]
+            if pos in self.junctions:
+                h, pending = self.junctions[pos].forward(batch, h, pending, x0), None
             if self._takes_next_norm[entry.layer]:
-                after = self.blocks[schedule[pos + 1].layer] if pos + 1 < len(schedule) else None
-                next_norm = self.final_norm if after is None else (after.first_norm() if hasattr(after, "first_norm") else None)
+                after = self.blocks[schedule[pos + 1].layer] if pos + 1 < len(schedule) and pos + 1 not in self.junctions else None
+                next_norm = self.final_norm if pos + 1 == len(schedule) else (after.first_norm() if hasattr(after, "first_norm") else None)
                 pending = block.forward(batch, h, pending, cache.view(pos), next_norm=next_norm)
             else:
                 pending = block.forward(batch, h, pending, cache.view(pos))

@@ -195,6 +195,28 @@ def add_rows(h: torch.Tensor, delta: torch.Tensor) -> None:
     _check(_lib.gb_add_rows(_ptr(h), _ptr(delta), c_int(h.shape[0]), c_int(h.shape[1]), _stream()))
 
 
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """out[r] += bias, float32 rows: the bias of a projection whose product left float32."""
+    _need(out, "rows", torch.float32, 2)
+    _need(bias, "bias", torch.float32, 1)
+    if bias.numel() != out.shape[1]:
+        raise KernelError(f"add_bias: a bias of {bias.numel()} for rows of {out.shape[1]}")
+    _check(_lib.gb_add_bias(_ptr(out), _ptr(bias), c_int(out.shape[0]), c_int(out.shape[1]), _stream()))
+
+
+def concat_cast(h: torch.Tensor, delta: Optional[torch.Tensor], side: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = [h[r] (+ delta[r]) | side[r]] in ``out``'s dtype: two float32 rows side by side as one product's input."""
+    _need(h, "residual", torch.float32, 2)
+    _need(side, "second rows", torch.float32, 2)
+    _need(out, "joined rows", dim=2)
+    if delta is not None:
+        _need(delta, "delta", torch.float32, 2)
+    rows, n = h.shape
+    if side.shape != h.shape or out.shape != (rows, 2 * n) or (delta is not None and delta.shape != h.shape):
+        raise KernelError(f"concat_cast: {tuple(h.shape)} and {tuple(side.shape)} into {tuple(out.shape)}")
+    _check(_lib.gb_concat_cast(_ptr(h), _ptr(delta), _ptr(side), _ptr(out), _code(out.dtype), c_int(rows), c_int(n), _stream()))
+
+
 # ---- feed-forward activation -------------------------------------------------------------
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleave8: bool = False) -> None:
     """out[r, i] = silu(gate[r, i]) * up[r, i]; gate and up are the two halves of ``gate_up``'s
@@ -495,7 +517,7 @@ class _QkRopeParams(Structure):
         ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
         ("write_kv", c_int), ("rows", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("pages", c_int), ("max_slots", c_int),
-        ("q_b", c_void_p), ("k_b", c_void_p), ("v_b", c_void_p), ("pairs", c_int), ("dv", c_int),
+        ("q_b", c_void_p), ("k_b", c_void_p), ("v_b", c_void_p), ("pairs", c_int), ("dv", c_int), ("span", c_int),
     ]
 
 
@@ -505,15 +527,16 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                  row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
                  block_table: torch.Tensor,
                  k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool,
-                 biases=None, pairs: bool = False, value_dim: Optional[int] = None) -> "_QkRopeParams":
+                 biases=None, pairs: bool = False, value_dim: Optional[int] = None, span: bool = False) -> "_QkRopeParams":
     """``biases`` = (q, k, v) float32 vectors or None each, added to the heads first; ``pairs``: channels
     2j and 2j + 1 turn together instead of j and j + rotary_dim / 2; ``value_dim``: size of a value
-    head if it is not ``head_dim``.  With any of them the rows may be wider than q, k and v (what
-    follows them is left alone)."""
+    head if it is not ``head_dim``; ``span``: the norm runs over all heads of q together (``q_weight`` of
+    heads * head_dim) and over all heads of k together, not per head.  With any of them the rows may be
+    wider than q, k and v (what follows them is left alone)."""
     _need(qkv, "qkv", dim=2, contiguous=False)
     rows = qkv.shape[0]
     dv = head_dim if value_dim is None else int(value_dim)
-    general = biases is not None or pairs or dv != head_dim
+    general = biases is not None or pairs or dv != head_dim or span
     used = (heads + kv_heads) * head_dim + kv_heads * dv
     if qkv.stride(1) != 1 or (qkv.shape[1] < used if general else (qkv.shape[1] != used or not qkv.is_contiguous())):
         raise KernelError(f"qk_norm_rope: qkv {tuple(qkv.shape)} for {heads}+{kv_heads} heads of {head_dim} and {kv_heads} of {dv}")
@@ -523,11 +546,11 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
             _need(t, nm, torch.float32, 1)
             if t.numel() != n:
                 raise KernelError(f"qk_norm_rope: {nm} has {t.numel()} elements, want {n}")
-    for t, nm in ((q_weight, "q norm"), (k_weight, "k norm")):
+    for t, nm, n in ((q_weight, "q norm", heads * head_dim if span else head_dim), (k_weight, "k norm", kv_heads * head_dim if span else head_dim)):
         if t is not None:
             _need(t, nm, torch.float32, 1)
-            if t.numel() != head_dim:
-                raise KernelError(f"qk_norm_rope: {nm} weight has {t.numel()} elements, head_dim is {head_dim}")
+            if t.numel() != n:
+                raise KernelError(f"qk_norm_rope: {nm} weight has {t.numel()} elements, want {n}")
     table_positions = 0
     if rotary_dim > 0:
         _need(cos, "rope cos", torch.float32, 2)
@@ -552,7 +575,7 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                       1 if write_kv else 0, rows, heads, kv_heads, head_dim,
                       0 if k_plane is None else k_plane.shape[0], block_table.shape[0],
                       0 if q_b is None else q_b.data_ptr(), 0 if k_b is None else k_b.data_ptr(),
-                      0 if v_b is None else v_b.data_ptr(), 1 if pairs else 0, dv)
+                      0 if v_b is None else v_b.data_ptr(), 1 if pairs else 0, dv, 1 if span else 0)
     return p
 
 
@@ -572,7 +595,7 @@ class _AttnParams(Structure):
         ("seq_slot", c_void_p), ("seq_q_start", c_void_p), ("seq_q_len", c_void_p),
         ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
-        ("pages", c_int), ("max_slots", c_int), ("dv", c_int), ("keep_first", c_int), ("sink", c_int),
+        ("pages", c_int), ("max_slots", c_int), ("dv", c_int), ("keep_first", c_int), ("sink", c_int), ("sinks", c_void_p),
     ]
 
 
@@ -585,9 +608,10 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
                  seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
                  heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
                  num_splits: int, scratch: Optional[torch.Tensor], value_dim: Optional[int] = None, keep_first: int = 0,
-                 sink: bool = False) -> "_AttnParams":
+                 sink: bool = False, sinks: Optional[torch.Tensor] = None) -> "_AttnParams":
     """``value_dim``: size of a value head if it is not ``head_dim``; ``keep_first``: with a window, keys
-    at positions below it stay visible; ``sink``: one more unit in the softmax denominator."""
+    at positions below it stay visible; ``sink``: one more unit in the softmax denominator; ``sinks``
+    (float32 [heads]): head h's denominator holds exp(sinks[h]) instead of that unit."""
     _need(q, "attention q", dim=2, contiguous=False)
     _need(out, "attention out", q.dtype, 2, contiguous=False)
     dv = head_dim if value_dim is None else int(value_dim)
@@ -595,6 +619,10 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
         raise KernelError(f"attention: q {tuple(q.shape)}, out {tuple(out.shape)} for {heads} heads of {head_dim} / {dv}")
     if keep_first < 0:
         raise KernelError(f"attention: {keep_first} kept first tokens")
+    if sinks is not None:
+        _need(sinks, "sink scores", torch.float32, 1)
+        if sinks.numel() != heads:
+            raise KernelError(f"attention: {sinks.numel()} sink scores for {heads} heads")
     for t, nm, n in ((k_plane, "key plane", head_dim), (v_plane, "value plane", dv)):
         _need(t, nm, q.dtype, 4)
         if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != n:
@@ -616,7 +644,7 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr(),
                     k_plane.shape[0], block_table.shape[0], 0 if dv == head_dim else dv, int(keep_first) if window > 0 else 0,
-                    1 if sink else 0)
+                    1 if sink or sinks is not None else 0, 0 if sinks is None else sinks.data_ptr())
     return p
 
 
@@ -625,11 +653,11 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
               seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
               heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
               num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto",
-              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False) -> str:
+              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False, sinks: Optional[torch.Tensor] = None) -> str:
     """Causal GQA over the paged cache.  q is a [rows, >= heads*head_dim] view (row stride free),
     out is [rows, heads*value_dim].  Returns the kernel's name."""
     p = _attn_params(q, out, k_plane, v_plane, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, nseq, max_q_len,
-                     heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink)
+                     heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink, sinks)
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
         algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo_x(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
@@ -1176,19 +1204,25 @@ def attention_sigmoid(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor,
 # ---- mixture of experts -----------------------------------------------------------------------
 class _MoeRouteParams(Structure):
     _fields_ = [("logits", c_void_p), ("logits_stride", c_int64), ("rows", c_int), ("experts", c_int), ("top", c_int),
-                ("renorm_eps", c_float), ("dense", c_void_p), ("index", c_void_p), ("weight", c_void_p)]
+                ("renorm_eps", c_float), ("dense", c_void_p), ("index", c_void_p), ("weight", c_void_p), ("score_kind", c_int), ("renorm", c_int)]
 
 
 class _MoeRowsParams(Structure):
     _fields_ = [("x", c_void_p), ("x_stride", c_int64), ("up", c_void_p), ("down", c_void_p), ("act", c_void_p), ("out", c_void_p),
                 ("out_stride", c_int64), ("index", c_void_p), ("weight", c_void_p), ("rows", c_int), ("experts", c_int), ("top", c_int),
-                ("ff", c_int), ("hidden", c_int)]
+                ("ff", c_int), ("hidden", c_int), ("act_kind", c_int), ("weight_input", c_int)]
 
 
-def moe_route(logits: torch.Tensor, top: int, renorm_eps: float, dense: torch.Tensor, index: torch.Tensor, weight: torch.Tensor) -> None:
-    """Per row of ``logits`` (float32 [rows, experts]): softmax over the experts, the ``top`` largest scores
-    chosen, their weights s / (sum of the chosen + renorm_eps) left in ``dense`` (float32 [rows, experts], zeros
-    elsewhere) and as pairs in ``index`` (int32 [rows, top]) and ``weight`` (float32 [rows, top])."""
+MOE_SCORES = {"softmax": 0, "sigmoid": 1}
+MOE_ACTS = {"relu2": 0, "swiglu": 1}
+
+
+def moe_route(logits: torch.Tensor, top: int, renorm_eps: float, dense: torch.Tensor, index: torch.Tensor, weight: torch.Tensor,
+              score: str = "softmax", renorm: bool = True) -> None:
+    """Per row of ``logits`` (float32 [rows, experts]): scores (softmax over the experts, or with ``score``
+    "sigmoid" the sigmoid of each logit by itself), the ``top`` largest chosen, their weights s / (sum of the
+    chosen + renorm_eps), or with ``renorm`` False the scores themselves, left in ``dense`` (float32 [rows,
+    experts], zeros elsewhere) and as pairs in ``index`` (int32 [rows, top]) and ``weight`` (float32 [rows, top])."""
     _need(logits, "router logits", torch.float32, 2, contiguous=False)
     rows, experts = logits.shape
     _need(dense, "expert weights", torch.float32, 2)
@@ -1196,28 +1230,38 @@ def moe_route(logits: torch.Tensor, top: int, renorm_eps: float, dense: torch.Te
     _need(weight, "chosen weights", torch.float32, 2)
     if logits.stride(1) != 1 or dense.shape != (rows, experts) or index.shape != (rows, top) or weight.shape != (rows, top):
         raise KernelError(f"moe_route: logits {tuple(logits.shape)}, dense {tuple(dense.shape)}, pairs {tuple(index.shape)} / {tuple(weight.shape)}")
-    p = _MoeRouteParams(logits.data_ptr(), logits.stride(0), rows, experts, top, renorm_eps, dense.data_ptr(), index.data_ptr(), weight.data_ptr())
+    p = _MoeRouteParams(logits.data_ptr(), logits.stride(0), rows, experts, top, renorm_eps, dense.data_ptr(), index.data_ptr(), weight.data_ptr(),
+                        MOE_SCORES[score], 1 if renorm else 0)
     _check(_lib.gb_moe_route(byref(p), _stream()))
 
 
-def moe_act(up: torch.Tensor, dense: torch.Tensor, act: torch.Tensor, experts: int, ff: int) -> None:
-    """act[r, e * ff + i] = dense[r, e] * relu(up[r, e * ff + i])^2 (``act`` may be ``up``)."""
+def moe_act(up: torch.Tensor, dense: Optional[torch.Tensor], act: torch.Tensor, experts: int, ff: int, kind: str = "relu2",
+            weight_input: bool = False) -> None:
+    """act[r, e * ff + i] = dense[r, e] * relu(up[r, e * ff + i])^2 (``act`` may be ``up``).  ``kind`` "swiglu": ``up``
+    holds, for each expert, ff gate columns and then ff up columns, and the activation is silu(gate) * up (``act`` is
+    then another tensor).  ``weight_input``: the weight multiplies the expert's input (its products) instead of its
+    result.  ``dense`` None: weights of 1."""
     _need(up, "expert pre-activations", dim=2, contiguous=False)
     _need(act, "expert activations", up.dtype, 2, contiguous=False)
-    _need(dense, "expert weights", torch.float32, 2)
+    if dense is not None:
+        _need(dense, "expert weights", torch.float32, 2)
     rows = up.shape[0]
-    if up.shape != (rows, experts * ff) or act.shape != up.shape or dense.shape != (rows, experts) or up.stride(1) != 1 or act.stride(1) != 1:
-        raise KernelError(f"moe_act: up {tuple(up.shape)}, act {tuple(act.shape)}, weights {tuple(dense.shape)} for {experts} experts of {ff}")
-    _check(_lib.gb_moe_act(_ptr(up), c_int64(up.stride(0)), _ptr(dense), _ptr(act), c_int64(act.stride(0)), c_int(rows), c_int(experts),
-                           c_int(ff), _code(up.dtype), _stream()))
+    per = 2 if kind == "swiglu" else 1
+    if (up.shape != (rows, experts * ff * per) or act.shape != (rows, experts * ff) or (dense is not None and dense.shape != (rows, experts))
+            or up.stride(1) != 1 or act.stride(1) != 1 or (per == 2 and act.data_ptr() == up.data_ptr())):
+        raise KernelError(f"moe_act: up {tuple(up.shape)}, act {tuple(act.shape)} for {experts} experts of {ff} ({kind})")
+    _check(_lib.gb_moe_act_kind(_ptr(up), c_int64(up.stride(0)), _ptr(dense), _ptr(act), c_int64(act.stride(0)), c_int(rows), c_int(experts),
+                                c_int(ff), c_int(MOE_ACTS[kind]), c_int(1 if weight_input else 0), _code(up.dtype), _stream()))
 
 
 def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-             experts: int, ff: int) -> None:
+             experts: int, ff: int, kind: str = "relu2", weight_input: bool = False) -> None:
     """The experts' feed-forward for a step of few rows, reading only the chosen experts' matrices:
     out[r] = sum_k weight[r, k] * down_e(relu(up_e x[r])^2), e = index[r, k].  ``up`` is [experts * ff, hidden]
     (the up matrices one above the other), ``down`` [hidden, experts * ff] (the down matrices side by side),
-    ``out`` float32 [rows, hidden]."""
+    ``out`` float32 [rows, hidden].  ``kind`` "swiglu": gated experts, ``up`` [experts * 2 ff, hidden] with each
+    expert's gate rows ahead of its up rows; ``weight_input``: the weight multiplies the expert's input."""
+    per = 2 if kind == "swiglu" else 1
     _need(x, "moe x", dim=2, contiguous=False)
     _need(up, "stacked up matrices", dim=2)
     _need(down, "stacked down matrices", up.dtype, 2)
@@ -1226,20 +1270,25 @@ def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch
     _need(weight, "chosen weights", torch.float32, 2)
     rows, hidden = x.shape
     top = index.shape[1]
-    if (up.shape != (experts * ff, hidden) or down.shape != (hidden, experts * ff) or out.shape != (rows, hidden) or x.stride(1) != 1
+    if (up.shape != (experts * ff * per, hidden) or down.shape != (hidden, experts * ff) or out.shape != (rows, hidden) or x.stride(1) != 1
             or out.stride(1) != 1 or index.shape[0] != rows or weight.shape != index.shape):
         raise KernelError(f"moe_rows: x {tuple(x.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, out {tuple(out.shape)}")
     act = torch.empty((rows, top, ff), dtype=x.dtype, device=x.device)
     p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), out.data_ptr(), out.stride(0),
-                       index.data_ptr(), weight.data_ptr(), rows, experts, top, ff, hidden)
+                       index.data_ptr(), weight.data_ptr(), rows, experts, top, ff, hidden, MOE_ACTS[kind], 1 if weight_input else 0)
     _check(_lib.gb_moe_rows(byref(p), _code(x.dtype), _code(up.dtype), _stream()), 2)
 
 
 def moe_rows_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, offsets: torch.Tensor, src_row: torch.Tensor, ys: torch.Tensor,
-                     experts: int, top: int, ff: int) -> None:
+                     experts: int, top: int, ff: int, kind: str = "relu2", sorted_weight: Optional[torch.Tensor] = None) -> None:
     """The few-row feed-forward with the (row, choice) pairs sorted by expert (``offsets`` and ``src_row`` from
     ``moe_group``): every expert's matrices are read once, ``ys`` (float32 [rows * top, hidden]) receives each pair's
-    output down_e(relu(up_e x)^2) at its sorted place; ``moe_combine`` adds a row's pairs up with their weights."""
+    output down_e(relu(up_e x)^2) at its sorted place; ``moe_combine`` adds a row's pairs up with their weights.
+    ``kind`` as for ``moe_rows``; ``sorted_weight`` (float32 [rows * top], the pairs' weights in sorted order): the
+    weight multiplies the expert's input here, and ``moe_combine`` then adds up without weights."""
+    per = 2 if kind == "swiglu" else 1
+    if sorted_weight is not None:
+        _need(sorted_weight, "sorted weights", torch.float32, 1)
     _need(x, "moe x", dim=2, contiguous=False)
     _need(up, "stacked up matrices", dim=2)
     _need(down, "stacked down matrices", up.dtype, 2)
@@ -1247,25 +1296,37 @@ def moe_rows_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, offs
     _need(offsets, "offsets", torch.int32, 1)
     _need(src_row, "source rows", torch.int32, 1)
     rows, hidden = x.shape
-    if (up.shape != (experts * ff, hidden) or down.shape != (hidden, experts * ff) or ys.shape != (rows * top, hidden) or x.stride(1) != 1
-            or offsets.numel() < experts + 1 or src_row.numel() < rows * top):
+    if (up.shape != (experts * ff * per, hidden) or down.shape != (hidden, experts * ff) or ys.shape != (rows * top, hidden) or x.stride(1) != 1
+            or offsets.numel() < experts + 1 or src_row.numel() < rows * top or (sorted_weight is not None and sorted_weight.numel() < rows * top)):
         raise KernelError(f"moe_rows_grouped: x {tuple(x.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, outputs {tuple(ys.shape)}")
     act = torch.empty((rows * top, ff), dtype=x.dtype, device=x.device)
-    p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), 0, 0, 0, 0, rows, experts, top, ff, hidden)
+    p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), 0, 0, 0,
+                       0 if sorted_weight is None else sorted_weight.data_ptr(), rows, experts, top, ff, hidden, MOE_ACTS[kind],
+                       0 if sorted_weight is None else 1)
     _check(_lib.gb_moe_rows_grouped(byref(p), _ptr(offsets), _ptr(src_row), _ptr(ys), _code(x.dtype), _code(up.dtype), _stream()), 2)
 
 
-def moe_group(index: torch.Tensor, experts: int, offsets: torch.Tensor, place: torch.Tensor, src_row: torch.Tensor) -> None:
+def moe_group(index: torch.Tensor, experts: int, offsets: torch.Tensor, place: torch.Tensor, src_row: torch.Tensor,
+              weight: Optional[torch.Tensor] = None, sorted_weight: Optional[torch.Tensor] = None) -> None:
     """Sort the (row, choice) pairs of ``index`` (int32 [rows, top]) by expert: ``offsets`` (int32 [experts + 1]) receives
     where each expert's group starts, ``place`` (int32 [rows * top]) each pair's position in the sorted order and
-    ``src_row`` (int32 [rows * top]) the row of the pair at each position."""
+    ``src_row`` (int32 [rows * top]) the row of the pair at each position.  With ``weight`` (float32 [rows, top]) and
+    ``sorted_weight`` (float32 [rows * top]) the pairs' weights are left in sorted order too."""
     _need(index, "chosen experts", torch.int32, 2)
     rows, top = index.shape
     for t, nm, n in ((offsets, "offsets", experts + 1), (place, "places", rows * top), (src_row, "source rows", rows * top)):
         _need(t, nm, torch.int32, 1)
         if t.numel() < n:
             raise KernelError(f"moe_group: {nm} has {t.numel()} entries, want {n}")
-    _check(_lib.gb_moe_group(_ptr(index), c_int(rows), c_int(top), c_int(experts), _ptr(offsets), _ptr(place), _ptr(src_row), _stream()))
+    if (weight is None) != (sorted_weight is None):
+        raise KernelError("moe_group: weights in and out go together")
+    if weight is not None:
+        _need(weight, "chosen weights", torch.float32, 2)
+        _need(sorted_weight, "sorted weights", torch.float32, 1)
+        if weight.shape != index.shape or sorted_weight.numel() < rows * top:
+            raise KernelError(f"moe_group: weights {tuple(weight.shape)} / {sorted_weight.numel()} for pairs {tuple(index.shape)}")
+    _check(_lib.gb_moe_group_weights(_ptr(index), c_int(rows), c_int(top), c_int(experts), _ptr(offsets), _ptr(place), _ptr(src_row),
+                                     _ptr(weight), _ptr(sorted_weight), _stream()))
 
 
 def moe_gather(x: torch.Tensor, src_row: torch.Tensor, xs: torch.Tensor) -> None:
@@ -1284,15 +1345,19 @@ def relu2(z: torch.Tensor) -> None:
     _check(_lib.gb_relu2(_ptr(z), c_int64(z.numel()), _code(z.dtype), _stream()))
 
 
-def moe_combine(ys: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r] = sum_k weight[r, k] * ys[place[r * top + k]], float32, in the order of k."""
+def moe_combine(ys: torch.Tensor, place: torch.Tensor, weight: Optional[torch.Tensor], out: torch.Tensor, top: Optional[int] = None) -> None:
+    """out[r] = sum_k weight[r, k] * ys[place[r * top + k]], float32, in the order of k (``weight`` None: the plain
+    sum of ``top`` outputs a row)."""
     _need(ys, "expert outputs", torch.float32, 2)
     _need(place, "places", torch.int32, 1)
-    _need(weight, "chosen weights", torch.float32, 2)
     _need(out, "moe out", torch.float32, 2, contiguous=False)
-    rows, top = weight.shape
+    if weight is not None:
+        _need(weight, "chosen weights", torch.float32, 2)
+        rows, top = weight.shape
+    else:
+        rows, top = out.shape[0], int(top)
     if out.shape != (rows, ys.shape[1]) or ys.shape[0] != rows * top or place.numel() < rows * top or out.stride(1) != 1:
-        raise KernelError(f"moe_combine: outputs {tuple(ys.shape)}, weights {tuple(weight.shape)}, out {tuple(out.shape)}")
+        raise KernelError(f"moe_combine: outputs {tuple(ys.shape)}, {rows} x {top} pairs, out {tuple(out.shape)}")
     _check(_lib.gb_moe_combine(_ptr(ys), _ptr(place), _ptr(weight), _ptr(out), c_int64(out.stride(0)), c_int(rows), c_int(top), c_int(ys.shape[1]),
                                _stream()))
 

@@ -10,6 +10,7 @@ from .hyper import HyperBlock
 from .linear_state import DecayState, MatrixMemory
 from .moe import MoE
 from .norm import RMSNorm
+from .reinject import Reinject
 from .rope import NoPosition, PairRotaryEmbedding, RotaryEmbedding
 from .sigmoid_attention import SigmoidAttention
 from .swiglu import SwiGLU
@@ -28,6 +29,7 @@ registry.register_feed_forward("swiglu", SwiGLU)
 registry.register_feed_forward("moe", MoE)
 registry.register_block("prenorm", PreNormBlock)
 registry.register_block("hyper", HyperBlock)
+registry.register_junction("reinject", Reinject)
 
 __all__ = ["Attention", "DecayState", "DeltaRule", "FeedForward", "GatedAttention", "HyperBlock", "KVStateRequest", "MatrixMemory", "MoE", "SigmoidAttention", "PairRotaryEmbedding", "KVRequest", "Mixer", "NoPosition", "Norm", "Part", "PositionEncoding",
-           "PreNormBlock", "RMSNorm", "RotaryEmbedding", "Runtime", "StateRequest", "SwiGLU", "TensorDecl"]
+           "PreNormBlock", "Reinject", "RMSNorm", "RotaryEmbedding", "Runtime", "StateRequest", "SwiGLU", "TensorDecl"]

@@ -1,11 +1,12 @@
-"""Grouped-query attention with a kept-first-tokens window, a softmax sink, biased projections, an
-output gate and, optionally, another layer's keys and values (``GatedAttentionSpec``).
+"""Grouped-query attention with a kept-first-tokens window, a softmax sink (a unit, or a learned score
+per head), biased projections, a norm of q and k (per head, or over the whole projection), an output gate
+and, optionally, another layer's keys and values (``GatedAttentionSpec``); each of them can be left off.
 
 Per row: q | k | v | g = x [Wq; Wk; Wv; Wg]^T in one product (a layer that reads another layer's
-cache has only q and g); biases, the position encoding of q and k and the cache write in one
-row-wise kernel; scores (q . k) * scale in float32 over the keys j <= i with i - j < window or
-j < keep_first, softmax with one more unit in the denominator; the heads, each ``value_dim`` wide,
-times sigmoid(g); out = ctx Wo^T.  Keys are cached after rotation, so a layer that shares them
+cache has only q and g); biases, the norm of q and k, their position encoding and the cache write in
+one row-wise kernel; scores (q . k) * scale in float32 over the keys j <= i with i - j < window or
+j < keep_first, softmax with one more term in the denominator; the heads, each ``value_dim`` wide,
+times sigmoid(g); out = ctx Wo^T (+ bo).  Keys are cached after rotation, so a layer that shares them
 rotates only its queries.
 """
 from __future__ import annotations
@@ -41,7 +42,16 @@ class GatedAttention(Attention):
                           TensorDecl(prefix + n["v"] + spec.bias_suffix, (vd,), role="vector")]
         if spec.gate:
             decls.append(TensorDecl(prefix + n["g"], (od, spec.hidden)))
+        if getattr(spec, "qk_norm", None) is not None:
+            span = bool(getattr(spec, "qk_norm_span", False))
+            decls.append(TensorDecl(prefix + n["q_norm"], (qd if span else spec.head_dim,), role="norm"))
+            if spec.own_kv:
+                decls.append(TensorDecl(prefix + n["k_norm"], (kd if span else spec.head_dim,), role="norm"))
+        if getattr(spec, "sink_learned", False):
+            decls.append(TensorDecl(prefix + n["sink"], (spec.heads,), role="vector"))
         decls.append(TensorDecl(prefix + n["o"], (spec.hidden, od)))
+        if getattr(spec, "out_bias", False):
+            decls.append(TensorDecl(prefix + n["o"] + spec.bias_suffix, (spec.hidden,), role="vector"))
         return decls
 
     @classmethod
@@ -68,6 +78,20 @@ class GatedAttention(Attention):
         self.biases = None
         if spec.bias:
             self.biases = (f32(n["q"]), f32(n["k"]) if spec.own_kv else None, f32(n["v"]) if spec.own_kv else None)
+        # the norm of q and k (float32 weights; with ``qk_norm_span`` one weight over all heads), the learned sink
+        # scores and the output projection's bias
+        self.q_norm = self.k_norm = self.sinks = self.o_bias = None
+        self.eps = 0.0
+        self.norm_span = bool(getattr(spec, "qk_norm_span", False))
+        if getattr(spec, "qk_norm", None) is not None:
+            self.q_norm = tensors[prefix + n["q_norm"]].to(torch.float32).contiguous()
+            if spec.own_kv:
+                self.k_norm = tensors[prefix + n["k_norm"]].to(torch.float32).contiguous()
+            self.eps = float(spec.qk_norm.eps)
+        if getattr(spec, "sink_learned", False):
+            self.sinks = tensors[prefix + n["sink"]].to(torch.float32).contiguous()
+        if getattr(spec, "out_bias", False):
+            self.o_bias = tensors[prefix + n["o"] + spec.bias_suffix].to(torch.float32).contiguous()
         self.position = registry.part_class("position", spec.position.kind)(spec.position, prefix, tensors, runtime)
         self.q_dim = spec.heads * spec.head_dim
         self.kv_heads_own = spec.kv_heads if spec.own_kv else 0
@@ -85,9 +109,13 @@ class GatedAttention(Attention):
 
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
         self.rt.ops.gemm_add(self._gated_heads(batch, x, cache), self.o, h)
+        if self.o_bias is not None:
+            self.rt.ops.add_bias(h, self.o_bias)
 
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
         self.rt.ops.gemm(self._gated_heads(batch, x, cache), self.o, out)
+        if self.o_bias is not None:
+            self.rt.ops.add_bias(out, self.o_bias)
 
     def folds_norm(self, rows: int, norm) -> bool:
         return False
@@ -121,15 +149,16 @@ class GatedAttention(Attention):
         qkvg = torch.empty((rows, self.qkv.shape[0]), dtype=x.dtype, device=x.device)
         ops.gemm(x, self.qkv, qkvg)
         cos, sin, rot = self.position.kernel_args()
-        ops.qk_norm_rope_kv_write(qkvg, s.heads, self.kv_heads_own, s.head_dim, None, None, 0.0, cos, sin, rot, batch.row_pos,
-                                  batch.row_seq, batch.seq_slot, cache.block_table, cache.k if s.own_kv else None,
+        ops.qk_norm_rope_kv_write(qkvg, s.heads, self.kv_heads_own, s.head_dim, self.q_norm, self.k_norm, self.eps, cos, sin, rot,
+                                  batch.row_pos, batch.row_seq, batch.seq_slot, cache.block_table, cache.k if s.own_kv else None,
                                   cache.v if s.own_kv else None, s.own_kv, biases=self.biases,
-                                  pairs=bool(getattr(self.position, "pairs", False)), value_dim=s.value_dim)
+                                  pairs=bool(getattr(self.position, "pairs", False)), value_dim=s.value_dim, span=self.norm_span)
         ctx = torch.empty((rows, self.o_dim), dtype=x.dtype, device=x.device)
         splits, scratch = self.key_splits(batch)
         ops.attention(qkvg, ctx, cache.k, cache.v, cache.block_table, batch.seq_slot, batch.seq_q_start, batch.seq_q_len,
                       batch.seq_kv_len, batch.nseq, batch.max_q_len, s.heads, s.kv_heads, s.head_dim, float(s.scale), int(s.window),
-                      splits, scratch, value_dim=s.value_dim, keep_first=int(s.keep_first), sink=bool(s.sink))
+                      splits, scratch, value_dim=s.value_dim, keep_first=int(s.keep_first), sink=bool(s.sink) or self.sinks is not None,
+                      sinks=self.sinks)
         if s.gate:
             ops.head_norm_gate(ctx, qkvg[:, self.g_off:self.g_off + self.o_dim], ctx, s.heads, s.value_dim, ops.GATE_SIGMOID)
         return ctx

@@ -1,5 +1,10 @@
 """Mixture-of-experts feed-forward (``MoESpec``): every token uses the ``top`` experts its router scores
-highest, out = sum over the chosen e of weight_e * down_e(relu(up_e x)^2).
+highest, out = sum over the chosen e of weight_e * down_e(relu(up_e x)^2).  The spec may ask for sigmoid scores,
+weights that are not renormalised, weights that multiply an expert's input (out = sum expert_e(weight_e x)), gated
+experts down_e(silu(gate_e x) * (up_e x)), whose gate and up matrices are then stacked expert by expert as
+[gate_e; up_e], and a shared expert that every token uses (a ``SwiGLU`` part of its own, added to the sum).
+An expert has no biases, so a weight on its input is a factor on the outputs of its first products: it is applied
+to them in float32, inside the activation between the two products.
 
 The router's logits are a float32 product and its softmax, choice and weights are float32
 (``ops.moe_route``).  The experts' matrices are kept stacked: all up matrices one above the other and all
@@ -21,6 +26,7 @@ from typing import List, Mapping
 import torch
 
 from .base import FeedForward, Runtime, TensorDecl
+from .swiglu import SwiGLU
 
 
 class MoE(FeedForward):
@@ -32,27 +38,50 @@ class MoE(FeedForward):
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
         decls = [TensorDecl(prefix + "router", (spec.experts, spec.hidden))]
         for e in range(spec.experts):
+            if getattr(spec, "act", "relu2") == "swiglu":
+                decls.append(TensorDecl(prefix + f"e{e}.gate", (spec.intermediate, spec.hidden)))
             decls += [TensorDecl(prefix + f"e{e}.up", (spec.intermediate, spec.hidden)),
                       TensorDecl(prefix + f"e{e}.down", (spec.hidden, spec.intermediate))]
+        shared = getattr(spec, "shared", None)
+        if shared is not None:
+            decls += SwiGLU.declare(shared, prefix + spec.shared_prefix)
         return decls
 
     def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.spec = spec
         self.rt = runtime
+        self.act = getattr(spec, "act", "relu2")
+        self.score = getattr(spec, "score", "softmax")
+        self.renorm = bool(getattr(spec, "renorm", True))
+        self.weight_input = getattr(spec, "weight_on", "output") == "input"
+        if self.act not in ("relu2", "swiglu") or self.score not in ("softmax", "sigmoid") or getattr(spec, "weight_on", "output") not in ("output", "input"):
+            raise ValueError(f"{prefix}: unknown activation, score or weight placement in {spec}")
         ups = [tensors[prefix + f"e{e}.up"] for e in range(spec.experts)]
+        if self.act == "swiglu":     # a gated expert's rows: its gate matrix, then its up matrix
+            ups = [t for e in range(spec.experts) for t in (tensors[prefix + f"e{e}.gate"], ups[e])]
         downs = [tensors[prefix + f"e{e}.down"] for e in range(spec.experts)]
         if len({t.dtype for t in ups + downs}) != 1:
             raise ValueError(f"{prefix}: the experts are stored in different dtypes; they must agree")
         self.up = torch.cat(ups, dim=0).contiguous()         # [experts * ff, hidden]
         self.down = torch.cat(downs, dim=1).contiguous()     # [hidden, experts * ff]
         self.router = tensors[prefix + "router"].contiguous()
+        shared = getattr(spec, "shared", None)
+        self.shared = None if shared is None else SwiGLU(shared, prefix + spec.shared_prefix, tensors, runtime)
 
     def weight_bytes(self) -> int:
         """Bytes of the matrices a token's step reads: the router and the chosen experts."""
         per = (self.up.numel() + self.down.numel()) * self.up.element_size() // self.spec.experts
-        return self.router.numel() * self.router.element_size() + per * self.spec.top
+        shared = 0 if self.shared is None else self.shared.weight_bytes()
+        return self.router.numel() * self.router.element_size() + per * self.spec.top + shared
 
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
+        self._experts(batch, x, out)
+        if self.shared is not None:
+            both = torch.empty_like(out)
+            self.shared.forward(batch, x, both)
+            self.rt.ops.add_rows(out, both)
+
+    def _experts(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
         ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
         logits = torch.empty((rows, s.experts), dtype=torch.float32, device=x.device)
@@ -60,27 +89,30 @@ class MoE(FeedForward):
         dense = torch.empty((rows, s.experts), dtype=torch.float32, device=x.device)
         index = torch.empty((rows, s.top), dtype=torch.int32, device=x.device)
         weight = torch.empty((rows, s.top), dtype=torch.float32, device=x.device)
-        ops.moe_route(logits, s.top, float(s.renorm_eps), dense, index, weight)
+        ops.moe_route(logits, s.top, float(s.renorm_eps), dense, index, weight, score=self.score, renorm=self.renorm)
         if rows <= self.ROWS_SPARSE and s.top < s.experts:
             if rows * s.top <= s.experts:      # hardly two pairs with one expert: a pair reads its expert's matrices
-                ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate)
+                ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate, kind=self.act, weight_input=self.weight_input)
                 return
             # more pairs than experts: sorted by expert on the device, every expert's matrices are read once
             pairs = rows * s.top
             offsets = torch.empty(s.experts + 1, dtype=torch.int32, device=x.device)
             place = torch.empty(pairs, dtype=torch.int32, device=x.device)
             src_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
-            ops.moe_group(index, s.experts, offsets, place, src_row)
+            sorted_w = torch.empty(pairs, dtype=torch.float32, device=x.device) if self.weight_input else None
+            ops.moe_group(index, s.experts, offsets, place, src_row, weight if self.weight_input else None, sorted_w)
             ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
-            ops.moe_rows_grouped(x, self.up, self.down, offsets, src_row, ys, s.experts, s.top, s.intermediate)
-            ops.moe_combine(ys, place, weight, out)
+            ops.moe_rows_grouped(x, self.up, self.down, offsets, src_row, ys, s.experts, s.top, s.intermediate, kind=self.act,
+                                 sorted_weight=sorted_w)
+            ops.moe_combine(ys, place, None if self.weight_input else weight, out, top=s.top)
             return
         if rows >= self.ROWS_GROUPED and s.top < s.experts and not torch.cuda.is_current_stream_capturing():
             self._grouped(x, index, weight, out)
             return
-        act = torch.empty((rows, s.experts * s.intermediate), dtype=x.dtype, device=x.device)
-        ops.gemm(x, self.up, act)
-        ops.moe_act(act, dense, act, s.experts, s.intermediate)
+        up = torch.empty((rows, self.up.shape[0]), dtype=x.dtype, device=x.device)
+        ops.gemm(x, self.up, up)
+        act = up if self.act == "relu2" else torch.empty((rows, s.experts * s.intermediate), dtype=x.dtype, device=x.device)
+        ops.moe_act(up, dense, act, s.experts, s.intermediate, kind=self.act, weight_input=self.weight_input)
         ops.gemm(act, self.down, out)
 
     def _grouped(self, x: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -90,19 +122,27 @@ class MoE(FeedForward):
         offsets = torch.empty(s.experts + 1, dtype=torch.int32, device=x.device)
         place = torch.empty(pairs, dtype=torch.int32, device=x.device)
         src_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
-        ops.moe_group(index, s.experts, offsets, place, src_row)
+        sorted_w = torch.empty(pairs, dtype=torch.float32, device=x.device) if self.weight_input else None
+        ops.moe_group(index, s.experts, offsets, place, src_row, weight if self.weight_input else None, sorted_w)
         bounds = offsets.tolist()               # the one host read of a prompt-sized step
         xs = torch.empty((pairs, s.hidden), dtype=x.dtype, device=x.device)
         ops.moe_gather(x, src_row, xs)
-        act = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+        per = self.up.shape[0] // s.experts     # rows of the stack an expert holds: ff, or gate and up
+        act = torch.empty((pairs, per), dtype=x.dtype, device=x.device)
         for e in range(s.experts):
             lo, hi = bounds[e], bounds[e + 1]
             if hi > lo:
-                ops.gemm_w_cols(xs[lo:hi], self.up[e * ff:(e + 1) * ff], act[lo:hi])
-        ops.relu2(act)
+                ops.gemm_w_cols(xs[lo:hi], self.up[e * per:(e + 1) * per], act[lo:hi])
+        if self.act == "relu2" and not self.weight_input:
+            ops.relu2(act)
+        else:
+            # every sorted pair is a row of one "expert" here: its own weight (or 1), its own activation
+            made = act if self.act == "relu2" else torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+            ops.moe_act(act, None if sorted_w is None else sorted_w.view(pairs, 1), made, 1, ff, kind=self.act, weight_input=self.weight_input)
+            act = made
         ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
         for e in range(s.experts):
             lo, hi = bounds[e], bounds[e + 1]
             if hi > lo:
                 ops.gemm_w_cols(act[lo:hi], self.down[:, e * ff:(e + 1) * ff], ys[lo:hi])
-        ops.moe_combine(ys, place, weight, out)
+        ops.moe_combine(ys, place, None if self.weight_input else weight, out, top=s.top)

@@ -27,6 +27,9 @@ class RMSNorm(Norm):
         offset = float(getattr(spec, "offset", 0.0))
         if offset != 0.0:
             self.weight = (self.weight + offset).contiguous()
+        gain = float(getattr(spec, "gain", 1.0))
+        if gain != 1.0:
+            self.weight = (self.weight * gain).contiguous()
         self.eps = float(spec.eps)
 
     def rms_fold(self):

@@ -16,7 +16,7 @@ import json
 import os
 from typing import Any, Callable, Dict, List, Optional, Type
 
-PART_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block")
+PART_CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "junction")
 
 _parts: Dict[str, Dict[str, type]] = {c: {} for c in PART_CATEGORIES}
 _architectures: Dict[str, type] = {}
@@ -64,6 +64,11 @@ def register_position(kind: str, cls: type) -> None:
 
 def register_block(kind: str, cls: type) -> None:
     register_part("block", kind, cls)
+
+
+def register_junction(kind: str, cls: type) -> None:
+    """A part that rewrites the residual between two runs of the schedule (``ScheduleEntry.enter``)."""
+    register_part("junction", kind, cls)
 
 
 def register_architecture(name: str, config_cls: type, model_type: Optional[str] = None) -> None:
@@ -119,9 +124,11 @@ def _register_builtin() -> None:
     from .config.qwen3 import Qwen3Config
     from .config.pugalix import PugalixConfig
     from .config.vepitar import VepitarConfig
+    from .config.kalonex import KalonexConfig
     register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
     register_architecture("Pugalix", PugalixConfig)
     register_architecture("Vepitar", VepitarConfig)
+    register_architecture("Kalonex", KalonexConfig)
 
 
 _register_builtin()

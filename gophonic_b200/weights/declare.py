@@ -24,6 +24,15 @@ def declare_model(spec) -> List[TensorDecl]:
                                           role="embedding")]
     for layer in spec.layers:
         decls += registry.part_class("block", layer.block).declare(layer)
+    # what the schedule's junctions resolve; positions that name the same tensor share it
+    named = {d.name for d in decls}
+    for entry in spec.schedule:
+        enter = getattr(entry, "enter", None)
+        if enter is not None:
+            for d in registry.part_class("junction", enter.kind).declare(enter, ""):
+                if d.name not in named:
+                    named.add(d.name)
+                    decls.append(d)
     decls += registry.part_class("norm", spec.final_norm.kind).declare(spec.final_norm, final_norm_prefix(spec))
     decls.append(TensorDecl(spec.head.name, (spec.head.vocab, spec.head.hidden), role="matrix",
                             optional=spec.head.tied_to is not None))
