@@ -484,7 +484,8 @@ def test_mixture_rows(rows, sizes, dtype):
         # a row whose last chosen score nearly ties with the next may take another expert in bfloat16
         s = np.sort(P.sigmoid(x @ w["router"].T), axis=-1)[:, ::-1]
         sure = np.ones(rows, bool) if top == experts else (s[:, top - 1] - s[:, top]) > 0.02
-        close(got[sure], want[sure], 3e-2)
+        if sure.any():
+            close(got[sure], want[sure], 3e-2)
 
 
 # ---- generation through the entry point, the trace program, the command line ----------------------
