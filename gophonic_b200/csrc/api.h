@@ -149,6 +149,12 @@ GB_API int gb_gemm_tc5_pair_swiglu(const void* A, const void* W, void* C, int c_
                                    cudaStream_t stream);
 GB_API int gb_gemm_tc5_ldw(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc,
                            int pair, cudaStream_t stream);
+// Products of groups of rows (sorted by group, bounds in `offsets` on the device) with their own weight blocks, in
+// one launch: block e of W is rows e * w_rows .. (by_cols 0; gated: N gate rows then N up rows, and the output is
+// silu(f g) * (f u) with f = row_weight[row]) or columns e * K .. (by_cols 1).  With row_map, row r lands in row row_map[r] of C.
+GB_API int gb_gemm_tc5_grouped(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
+                               int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
+                               const int* row_map, cudaStream_t stream);
 GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream);
 // most rows the products with the residual's row-wise work folded in take
 constexpr int GB_FOLD_MAX_ROWS = 64;

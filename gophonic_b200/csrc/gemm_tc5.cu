@@ -579,6 +579,260 @@ int launch(const void* A, const void* W, void* C, int M, int N, int K, int64_t l
     return 0;
 }
 
+// ---- one launch for the products of every group of rows ------------------------------------------
+// The rows of A are sorted by group (the experts of a mixture): group e owns rows offsets[e] .. offsets[e + 1] - 1
+// and has a weight block of its own, either rows e * w_rows .. of W (the same K for all) or columns e * K .. of W.
+// The sizes of the groups are known on the device only, so the CTAs walk one list of tiles, group after group with
+// the M tile fastest inside a group, that each role derives from `offsets` by itself; nothing is read on the host
+// and the launch can be captured.  A tile's rows beyond its group's end (the next group's rows, or zeros past the
+// end of A) are multiplied and not stored; with blocks of columns, the K steps beyond a block multiply zeros of A,
+// whose map ends with the block's width.  W comes in two boxes of 128 rows a stage.  Plain epilogue: C[row, n];
+// gated epilogue: the first box holds 128 gate rows and the second the 128 up rows of the same outputs, and the
+// tile writes C[row, n] = silu(f g) * (f u), f = row_weight[row] (1 without), for 128 outputs.  With `row_map` the
+// result of row r goes to row row_map[r] of C.
+struct GroupWalk {
+    int e = 0, base = 0, lo = 0, hi = 0, tm = 0;
+    // the group that holds tile `tile` (tiles are asked for in ascending order); false when the tiles are used up
+    __device__ __forceinline__ bool seek(const int* __restrict__ offsets, int groups, int tiles_n, int tile) {
+        while (e < groups) {
+            lo = offsets[e];
+            hi = offsets[e + 1];
+            tm = (hi - lo + BM - 1) / BM;
+            if (tile < base + tm * tiles_n) return true;
+            base += tm * tiles_n;
+            e++;
+        }
+        return false;
+    }
+};
+
+template <typename TC>
+__device__ __forceinline__ void store_gated32(TC* __restrict__ dst, int left, bool vec_ok, const uint32_t (&g)[32], const uint32_t (&u)[32],
+                                              float f) {
+    float act[32];
+#pragma unroll
+    for (int e = 0; e < 32; e++) {
+        const float a = f * __uint_as_float(g[e]), b = f * __uint_as_float(u[e]);
+        act[e] = __fdividef(a, 1.f + __expf(-a)) * b;
+    }
+    if (vec_ok && left >= 32) {
+        if (sizeof(TC) == 2) {
+            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                __nv_bfloat162 t0 = __floats2bfloat162_rn(act[e * 8 + 0], act[e * 8 + 1]);
+                __nv_bfloat162 t1 = __floats2bfloat162_rn(act[e * 8 + 2], act[e * 8 + 3]);
+                __nv_bfloat162 t2 = __floats2bfloat162_rn(act[e * 8 + 4], act[e * 8 + 5]);
+                __nv_bfloat162 t3 = __floats2bfloat162_rn(act[e * 8 + 6], act[e * 8 + 7]);
+                uint4 v;
+                v.x = *reinterpret_cast<uint32_t*>(&t0);
+                v.y = *reinterpret_cast<uint32_t*>(&t1);
+                v.z = *reinterpret_cast<uint32_t*>(&t2);
+                v.w = *reinterpret_cast<uint32_t*>(&t3);
+                d4[e] = v;
+            }
+        } else {
+            float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+            for (int e = 0; e < 8; e++) d4[e] = make_float4(act[e * 4], act[e * 4 + 1], act[e * 4 + 2], act[e * 4 + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++)
+            if (e < left) dst[e] = from_f32<TC>(act[e]);
+    }
+}
+
+template <typename TC>
+__global__ void __launch_bounds__(THREADS) gemm_tc5_grouped_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                  const __grid_constant__ CUtensorMap map_w, TC* __restrict__ C,
+                                                                  const int* __restrict__ offsets, int groups, int N, int K, int64_t ldc,
+                                                                  int w_rows, int by_cols, int gated, const float* __restrict__ row_weight,
+                                                                  const int* __restrict__ row_map) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KT = (K + BK - 1) / BK;
+    const int TN = gated ? BN / 2 : BN;  // outputs a tile makes
+    const int tiles_n = (N + TN - 1) / TN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        abort_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();  // the groups' bounds and the rows come from the kernels ahead
+    pdl_trigger();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool stop = false;
+            GroupWalk g;
+            for (int tile = blockIdx.x; !stop && g.seek(offsets, groups, tiles_n, tile); tile += gridDim.x) {
+                const int local = tile - g.base;
+                const int m0 = g.lo + (local % g.tm) * BM, nt = local / g.tm;
+                // the two boxes of W: rows and first K column
+                const int y0 = by_cols ? nt * BN : g.e * w_rows + nt * TN;
+                const int y1 = by_cols ? y0 + BN / 2 : (gated ? y0 + N : y0 + BN / 2);
+                const int xw = by_cols ? g.e * K : 0;
+                for (int kt = 0; kt < KT; kt++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1u)) {
+                        atomicCAS(&g_tc5_status, 0, 1);
+                        abort_s = 1;
+                    }
+                    if (*(volatile int*)&abort_s) {
+                        stop = true;
+                        break;
+                    }
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+                    tma_load_2d(st, &map_a, kt * BK, m0, &full_bar[s]);
+                    tma_load_2d(st + A_BYTES, &map_w, xw + kt * BK, y0, &full_bar[s]);
+                    tma_load_2d(st + A_BYTES + B_BYTES / 2, &map_w, xw + kt * BK, y1, &full_bar[s]);
+                }
+            }
+            if (stop) {
+                for (int j = it > STAGES ? it - STAGES : 0; j < it; j++) mbar_wait(&full_bar[j % STAGES], (uint32_t)(j / STAGES) & 1u);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = instr_desc(BM, BN);
+            int it = 0, i = 0;
+            bool stop = false;
+            GroupWalk g;
+            for (int tile = blockIdx.x; !stop && g.seek(offsets, groups, tiles_n, tile); tile += gridDim.x, i++) {
+                const int buf = i & 1;
+                const uint32_t use = (uint32_t)(i >> 1) & 1u;
+                if (!mbar_wait(&acc_empty[buf], use ^ 1u)) {
+                    atomicCAS(&g_tc5_status, 0, 4);
+                    abort_s = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+                for (int kt = 0; kt < KT; kt++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (uint32_t)(it / STAGES) & 1u;
+                    if (!mbar_wait(&full_bar[s], phase)) {
+                        atomicCAS(&g_tc5_status, 0, 2);
+                        abort_s = 1;
+                        stop = true;
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const uint32_t a_addr = s32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint64_t adesc = smem_desc(a_addr), bdesc = smem_desc(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++)
+                        umma(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kt > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&empty_bar[s]);
+                }
+                if (!stop) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const bool vec_ok = (ldc % 8 == 0) && (((uintptr_t)C & 15) == 0);
+        int i = 0;
+        GroupWalk g;
+        for (int tile = blockIdx.x; g.seek(offsets, groups, tiles_n, tile); tile += gridDim.x, i++) {
+            const int local = tile - g.base;
+            const int m0 = g.lo + (local % g.tm) * BM, n0 = (local / g.tm) * TN;
+            const int buf = i & 1;
+            const uint32_t use = (uint32_t)(i >> 1) & 1u;
+            const int row = m0 + quad * 32 + lane;
+            const bool mine = row < g.hi;
+            const int crow = !mine ? 0 : (row_map ? row_map[row] : row);
+            const float f = (mine && row_weight) ? row_weight[row] : 1.f;
+            if (!mbar_wait(&acc_full[buf], use)) {
+                atomicCAS(&g_tc5_status, 0, 3);
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < TN; c0 += 32) {
+                if (n0 + c0 >= N) break;  // uniform across the warp
+                uint32_t r[32];
+                tmem_ld32(t_addr + (uint32_t)c0, r);
+                if (gated) {
+                    uint32_t u[32];
+                    tmem_ld32(t_addr + (uint32_t)(BN / 2 + c0), u);
+                    if (mine) store_gated32<TC>(C + (int64_t)crow * ldc + n0 + c0, N - (n0 + c0), vec_ok, r, u, f);
+                } else {
+                    store_cols32<TC>(C, ldc, crow, mine ? 0x7fffffff : 0, N, n0 + c0, r, 0, vec_ok);
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <typename TC>
+int launch_grouped(const void* A, const void* W, void* C, const int* offsets, int groups, int P, int N, int K, int64_t lda, int64_t ldw,
+                   int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight, const int* row_map, cudaStream_t stream) {
+    const int smem = STAGES * STAGE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_grouped_kernel<TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) GB_REFUSE("gemm_tc5_grouped: cannot reserve %d bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        configured = true;
+    }
+    CUtensorMap map_a, map_w;
+    if (int rc = tc5_make_map(&map_a, A, P, K, lda, BM)) return rc;
+    if (by_cols) {
+        if (int rc = tc5_make_map(&map_w, W, N, (int)((int64_t)groups * K), ldw, BN / 2)) return rc;
+    } else {
+        if (int rc = tc5_make_map(&map_w, W, (int)((int64_t)groups * w_rows), K, ldw, BN / 2)) return rc;
+    }
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    // the groups' sizes are not known here: every group may end with a tile that is partly empty
+    const int tn = gated ? BN / 2 : BN;
+    const int64_t most = ((int64_t)ceil_div(P, BM) + (groups < P ? groups : P)) * ceil_div(N, tn);
+    const int grid = most < sms ? (int)most : sms;
+    cudaError_t e = launch_pdl(gemm_tc5_grouped_kernel<TC>, dim3(grid), dim3(THREADS), (size_t)smem, stream, map_a, map_w, (TC*)C, offsets,
+                               groups, N, K, ldc, w_rows, by_cols, gated, row_weight, row_map);
+    if (e != cudaSuccess) GB_REFUSE("gemm_tc5_grouped: launch failed: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 }  // namespace
 
 static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, int epi, int pair,
@@ -633,6 +887,31 @@ GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, in
 GB_API int gb_gemm_tc5_swiglu(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc,
                               cudaStream_t stream) {
     return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, 1, 0, stream);
+}
+
+// Products of groups of rows with their own weight blocks, in one launch (gemm_tc5_grouped_kernel): rows
+// offsets[e] .. offsets[e + 1] - 1 of A[P, K] (sorted by group; offsets[groups] <= P, on the device) times block e of W.
+// by_cols 0: block e is rows e * w_rows .. e * w_rows + N - 1 of W (gated: N gate rows, then N up rows; w_rows >= 2 N);
+// by_cols 1: block e is columns e * K .. e * K + K - 1 of W[N, groups * K].  C[row, 0 .. N - 1], or row row_map[row] of C.
+GB_API int gb_gemm_tc5_grouped(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
+                               int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
+                               const int* row_map, cudaStream_t stream) {
+    if (P <= 0 || N <= 0 || groups <= 0) return 0;
+    if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5_grouped: K = %d must be a positive multiple of 8", K);
+    if ((lda & 7) || lda < K) GB_REFUSE("gemm_tc5_grouped: row stride %lld of A must be a multiple of 8 and at least K", (long long)lda);
+    if ((ldw & 7) || ldw < (by_cols ? (int64_t)groups * K : (int64_t)K))
+        GB_REFUSE("gemm_tc5_grouped: row stride %lld of W must be a multiple of 8 and hold its blocks", (long long)ldw);
+    if (!by_cols && w_rows < (gated ? 2 * N : N)) GB_REFUSE("gemm_tc5_grouped: a block of %d rows does not hold %d outputs", w_rows, N);
+    if (by_cols && gated) GB_REFUSE("gemm_tc5_grouped: gated outputs come from blocks of rows");
+    if ((int64_t)groups * (by_cols ? K : w_rows) > 0x7fffffff) GB_REFUSE("gemm_tc5_grouped: W is too large");
+    if (ldc < N) GB_REFUSE("gemm_tc5_grouped: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5_grouped: operands must be 16-byte aligned");
+    if (c_dtype == GB_F32)
+        return launch_grouped<float>(A, W, C, offsets, groups, P, N, K, lda, ldw, ldc, w_rows, by_cols, gated, row_weight, row_map, stream);
+    if (c_dtype == GB_BF16)
+        return launch_grouped<__nv_bfloat16>(A, W, C, offsets, groups, P, N, K, lda, ldw, ldc, w_rows, by_cols, gated, row_weight, row_map,
+                                             stream);
+    GB_REFUSE("gemm_tc5_grouped: unknown output dtype %d", c_dtype);
 }
 
 // 0 if no tcgen05 kernel has given up on a barrier since the last call; else the role that did

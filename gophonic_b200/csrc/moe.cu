@@ -47,9 +47,11 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
 #pragma unroll
     for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++) {
         const int i = lane + 32 * e;
-        // scores are not negative; -1 marks what is absent or taken
-        s[e] = i < E ? (p.score_kind == 1 ? 1.f / (1.f + expf(-s[e])) : expf(s[e] - mx)) : -1.f;
-        if (i < E) sum += s[e];
+        // the key an expert is chosen by: its softmax numerator, or, for sigmoid scores, the logit itself (the
+        // sigmoid grows with it, and two large logits stay apart where their sigmoids both round to 1);
+        // -inf marks what is absent or taken
+        s[e] = i < E ? (p.score_kind == 1 ? s[e] : expf(s[e] - mx)) : -INFINITY;
+        if (i < E && p.score_kind != 1) sum += s[e];
     }
     sum = warp_sum(sum);
     const float inv = p.score_kind == 1 ? 1.f : 1.f / sum;     // a sigmoid score stands by itself
@@ -59,7 +61,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
     float my_w = 0.f;      // lane k keeps the k-th choice
     int my_i = 0;
     for (int k = 0; k < p.top; k++) {
-        float best = -1.f;
+        float best = -INFINITY;
         int best_i = 0x7fffffff;
 #pragma unroll
         for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++) {
@@ -74,8 +76,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
         }
 #pragma unroll
         for (int e = 0; e < MAX_EXPERTS_PER_LANE; e++)
-            if (lane + 32 * e == best_i) s[e] = -1.f;
-        const float sc = best * inv;
+            if (lane + 32 * e == best_i) s[e] = -INFINITY;
+        const float sc = p.score_kind == 1 ? 1.f / (1.f + expf(-best)) : best * inv;
         chosen_sum += sc;
         if (lane == (k & 31)) my_w = sc, my_i = best_i;
         if (k >= 32 && lane == 0) {}   // more than 32 choices are refused on the host

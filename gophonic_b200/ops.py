@@ -1382,3 +1382,48 @@ def gemm_w_cols(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> str:
     _check(_lib.gb_gemm_tc5_ldw(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K), c_int64(a.stride(0)),
                                 c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(1 if pair else 0), _stream()))
     return "tc5_pair" if pair else "tc5"
+
+
+def gemm_grouped_fits(a_dtype, w: torch.Tensor, K: int, by_cols: bool) -> bool:
+    """Whether ``gemm_grouped`` takes these operands: bfloat16, rows and blocks that start on 16 bytes."""
+    return (a_dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, groups: int, *, by_cols: bool = False,
+                 gated: bool = False, row_weight: Optional[torch.Tensor] = None, row_map: Optional[torch.Tensor] = None) -> None:
+    """One launch for the products of every group of rows: rows ``offsets[e] .. offsets[e + 1] - 1`` of ``a`` [P, K]
+    (sorted by group; ``offsets`` int32 [groups + 1] on the device, never read on the host) times block e of ``w``.
+    ``by_cols`` False: ``w`` is [groups * block, K] and block e its rows e * block ..; with ``gated`` a block is N gate
+    rows, then N up rows, and out = silu(f g) * (f u), f = ``row_weight[row]`` (1 if absent).  ``by_cols`` True: ``w`` is
+    [N, groups * K] and block e its columns e * K ...  ``out`` is [*, N]; with ``row_map`` (int32 [P]) the result of
+    row r is written to row ``row_map[r]`` of ``out``, otherwise to row r."""
+    _need(a, "grouped gemm a", torch.bfloat16, 2, contiguous=False)
+    _need(w, "grouped gemm w", torch.bfloat16, 2, contiguous=False)
+    _need(out, "grouped gemm out", dim=2, contiguous=False)
+    _need(offsets, "group offsets", torch.int32, 1)
+    P, K = a.shape
+    N = out.shape[1]
+    if offsets.numel() < groups + 1 or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm_grouped: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, {offsets.numel()} offsets")
+    if by_cols:
+        if gated or w.shape != (N, groups * K):
+            raise KernelError(f"gemm_grouped: w {tuple(w.shape)} is not [{N}, {groups} x {K}]")
+        block = 0
+    else:
+        if w.shape[0] % groups or w.shape[1] != K or w.shape[0] // groups != (2 * N if gated else N):
+            raise KernelError(f"gemm_grouped: w {tuple(w.shape)} is not {groups} blocks of {2 * N if gated else N} rows of {K}")
+        block = w.shape[0] // groups
+    if row_map is None and out.shape[0] < P:
+        raise KernelError(f"gemm_grouped: out has {out.shape[0]} rows for {P}")
+    if row_weight is not None:
+        _need(row_weight, "row weights", torch.float32, 1)
+        if row_weight.numel() < P or not gated:
+            raise KernelError("gemm_grouped: row weights go with gated outputs, one a row")
+    if row_map is not None:
+        _need(row_map, "row map", torch.int32, 1)
+        if row_map.numel() < P:
+            raise KernelError(f"gemm_grouped: {row_map.numel()} mapped rows for {P}")
+    _check(_lib.gb_gemm_tc5_grouped(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), _ptr(offsets), c_int(groups), c_int(P), c_int(N), c_int(K),
+                                    c_int64(a.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(block), c_int(1 if by_cols else 0),
+                                    c_int(1 if gated else 0), _ptr(row_weight), _ptr(row_map), _stream()))

@@ -106,7 +106,7 @@ class MoE(FeedForward):
                                  sorted_weight=sorted_w)
             ops.moe_combine(ys, place, None if self.weight_input else weight, out, top=s.top)
             return
-        if rows >= self.ROWS_GROUPED and s.top < s.experts and not torch.cuda.is_current_stream_capturing():
+        if rows >= self.ROWS_GROUPED and s.top < s.experts and (self._one_launch(x.dtype) or not torch.cuda.is_current_stream_capturing()):
             self._grouped(x, index, weight, out)
             return
         up = torch.empty((rows, self.up.shape[0]), dtype=x.dtype, device=x.device)
@@ -116,7 +116,7 @@ class MoE(FeedForward):
         ops.gemm(act, self.down, out)
 
     def _grouped(self, x: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-        """Every expert on its own rows: sort the pairs by expert, gather, two products an expert, add up."""
+        """Every expert on its own rows: sort the pairs by expert, gather, two products over the groups, add up."""
         ops, s = self.rt.ops, self.spec
         rows, pairs, ff = x.shape[0], x.shape[0] * s.top, s.intermediate
         offsets = torch.empty(s.experts + 1, dtype=torch.int32, device=x.device)
@@ -124,25 +124,50 @@ class MoE(FeedForward):
         src_row = torch.empty(pairs, dtype=torch.int32, device=x.device)
         sorted_w = torch.empty(pairs, dtype=torch.float32, device=x.device) if self.weight_input else None
         ops.moe_group(index, s.experts, offsets, place, src_row, weight if self.weight_input else None, sorted_w)
-        bounds = offsets.tolist()               # the one host read of a prompt-sized step
         xs = torch.empty((pairs, s.hidden), dtype=x.dtype, device=x.device)
         ops.moe_gather(x, src_row, xs)
         per = self.up.shape[0] // s.experts     # rows of the stack an expert holds: ff, or gate and up
-        act = torch.empty((pairs, per), dtype=x.dtype, device=x.device)
-        for e in range(s.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                ops.gemm_w_cols(xs[lo:hi], self.up[e * per:(e + 1) * per], act[lo:hi])
-        if self.act == "relu2" and not self.weight_input:
-            ops.relu2(act)
+        one_launch = self._one_launch(x.dtype)
+        bounds = None
+        if one_launch and self.act == "swiglu":
+            # gate and up products, the pairs' weights and the activation in one kernel
+            act = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+            ops.gemm_grouped(xs, self.up, act, offsets, s.experts, gated=True, row_weight=sorted_w)
         else:
-            # every sorted pair is a row of one "expert" here: its own weight (or 1), its own activation
-            made = act if self.act == "relu2" else torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
-            ops.moe_act(act, None if sorted_w is None else sorted_w.view(pairs, 1), made, 1, ff, kind=self.act, weight_input=self.weight_input)
-            act = made
-        ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
-        for e in range(s.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                ops.gemm_w_cols(act[lo:hi], self.down[:, e * ff:(e + 1) * ff], ys[lo:hi])
+            act = torch.empty((pairs, per), dtype=x.dtype, device=x.device)
+            if one_launch:
+                ops.gemm_grouped(xs, self.up, act, offsets, s.experts)
+            else:
+                bounds = offsets.tolist()       # the one host read of such a step
+                for e in range(s.experts):
+                    lo, hi = bounds[e], bounds[e + 1]
+                    if hi > lo:
+                        ops.gemm_w_cols(xs[lo:hi], self.up[e * per:(e + 1) * per], act[lo:hi])
+            if self.act == "relu2" and not self.weight_input:
+                ops.relu2(act)
+            else:
+                # every sorted pair is a row of one "expert" here: its own weight (or 1), its own activation
+                made = act if self.act == "relu2" else torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+                ops.moe_act(act, None if sorted_w is None else sorted_w.view(pairs, 1), made, 1, ff, kind=self.act, weight_input=self.weight_input)
+                act = made
+        if one_launch:
+            if s.top == 1 and self.weight_input:
+                # every row has one pair and its weight is spent: the product's rows go straight to their places
+                ops.gemm_grouped(act, self.down, out, offsets, s.experts, by_cols=True, row_map=src_row)
+                return
+            ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
+            ops.gemm_grouped(act, self.down, ys, offsets, s.experts, by_cols=True)
+        else:
+            ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
+            if bounds is None:
+                bounds = offsets.tolist()
+            for e in range(s.experts):
+                lo, hi = bounds[e], bounds[e + 1]
+                if hi > lo:
+                    ops.gemm_w_cols(act[lo:hi], self.down[:, e * ff:(e + 1) * ff], ys[lo:hi])
         ops.moe_combine(ys, place, None if self.weight_input else weight, out, top=s.top)
+
+    def _one_launch(self, act_dtype) -> bool:
+        """Whether the tensor-core kernel that walks all groups in one launch takes this mixture's matrices."""
+        ops, s = self.rt.ops, self.spec
+        return (ops.gemm_grouped_fits(act_dtype, self.up, s.hidden, False) and ops.gemm_grouped_fits(act_dtype, self.down, s.intermediate, True))

@@ -488,6 +488,62 @@ def test_mixture_rows(rows, sizes, dtype):
             close(got[sure], want[sure], 3e-2)
 
 
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("shape", [(5, 72, 40, [0, 3, 130, 0, 257]), (3, 300, 64, [1, 128, 129]), (7, 128, 200, [40, 0, 0, 9, 300, 64, 2]),
+                                   (1, 8, 8, [5]), (4, 520, 136, [127, 1, 256, 70])])
+def test_products_of_groups_of_rows_in_one_launch(shape, out_dtype):
+    """Rows sorted by group, every group times its own block of the weights (blocks of rows, gated blocks with a
+    weight a row, blocks of columns, rows written through a map), against one float64 product a group.  Groups that
+    are empty, smaller and larger than a tile, ending one row before and after a tile's edge."""
+    import torch
+    from gophonic_b200 import ops
+    ops.use_device(0)
+    dev = torch.device("cuda:0")
+    groups, N, K, counts = shape
+    assert len(counts) == groups
+    rng = np.random.default_rng(N + K)
+    P_rows = sum(counts)
+    bf = lambda a: torch.tensor(a, dtype=torch.float32).to(torch.bfloat16).to(dev)
+    f64 = lambda t: t.float().cpu().numpy().astype(np.float64)
+    td = torch.float32 if out_dtype == "float32" else torch.bfloat16
+    tol = 2e-3 if out_dtype == "float32" else 1.2e-2
+    a = bf(rng.standard_normal((P_rows + 3, K)))[:P_rows]            # rows beyond the last group exist and are not used
+    offsets = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32, device=dev)
+    lo = np.concatenate([[0], np.cumsum(counts)])
+    # blocks of rows
+    w = bf(rng.standard_normal((groups * N, K)) / np.sqrt(K))
+    out = torch.full((P_rows, N), 7.0, dtype=td, device=dev)
+    ops.gemm_grouped(a, w, out, offsets, groups)
+    want = np.concatenate([f64(a[lo[e]:lo[e + 1]]) @ f64(w[e * N:(e + 1) * N]).T for e in range(groups)])
+    close(out.float().cpu().numpy(), want, tol)
+    # gated blocks (N gate rows, then N up rows) with a weight on every row's input
+    wg = bf(rng.standard_normal((groups * 2 * N, K)) / np.sqrt(K))
+    f = torch.tensor(rng.uniform(0.2, 1.0, size=P_rows), dtype=torch.float32, device=dev)
+    for weights in (f, None):
+        out = torch.full((P_rows, N), 7.0, dtype=td, device=dev)
+        ops.gemm_grouped(a, wg, out, offsets, groups, gated=True, row_weight=weights)
+        rows = []
+        for e in range(groups):
+            x = f64(a[lo[e]:lo[e + 1]]) * (1.0 if weights is None else f64(f[lo[e]:lo[e + 1]])[:, None])
+            g, u = x @ f64(wg[e * 2 * N:e * 2 * N + N]).T, x @ f64(wg[e * 2 * N + N:(e + 1) * 2 * N]).T
+            rows.append(g * P.sigmoid(g) * u)
+        close(out.float().cpu().numpy(), np.concatenate(rows), tol)
+    # blocks of columns, rows written through a map (a permutation into a taller output)
+    wc = bf(rng.standard_normal((N, groups * K)) / np.sqrt(K))
+    perm = torch.tensor(rng.permutation(P_rows + 2)[:P_rows], dtype=torch.int32, device=dev)
+    want = np.concatenate([f64(a[lo[e]:lo[e + 1]]) @ f64(wc[:, e * K:(e + 1) * K]).T for e in range(groups)])
+    out = torch.full((P_rows, N), 7.0, dtype=td, device=dev)
+    ops.gemm_grouped(a, wc, out, offsets, groups, by_cols=True)
+    close(out.float().cpu().numpy(), want, tol)
+    out = torch.full((P_rows + 2, N), 7.0, dtype=td, device=dev)
+    ops.gemm_grouped(a, wc, out, offsets, groups, by_cols=True, row_map=perm)
+    got = out.float().cpu().numpy()
+    close(got[perm.cpu().numpy()], want, tol)
+    untouched = np.setdiff1d(np.arange(P_rows + 2), perm.cpu().numpy())
+    assert (got[untouched] == 7.0).all()
+    assert ops.tc5_status() == 0
+
+
 # ---- generation through the entry point, the trace program, the command line ----------------------
 def test_greedy_generation_through_the_entry_point(models):
     import gophonic_b200 as g
