@@ -515,6 +515,134 @@ __global__ void __launch_bounds__(256) qk_rope_span_kernel(QkRopeParamsX p) {
     }
 }
 
+// The same for bfloat16 rows whose heads, rotated halves and strides are multiples of eight elements: every thread
+// moves eight consecutive elements at a time (16-byte loads and stores), an element's partner in the rotation lies
+// a whole number of such pieces away, and a piece never straddles q and k or two heads.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 f = __bfloat1622float2(h[j]);
+        v[2 * j] = f.x, v[2 * j + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int j = 0; j < 4; j++) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    return out;
+}
+__device__ __forceinline__ void load8(const float* src, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+
+__global__ void __launch_bounds__(256) qk_rope_span_vec_kernel(QkRopeParamsX p) {
+    using T = __nv_bfloat16;
+    extern __shared__ __align__(16) float sh[];  // [heads * d + kv_heads * d] values, then [2][8] partial sums
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = blockIdx.x;
+    const int d = p.d, dv = p.dv > 0 ? p.dv : d;
+    const int nq = p.heads * d, nk = p.kv_heads * d, nv = p.kv_heads * dv;
+    float* y = sh;
+    float* part = sh + nq + nk;
+    T* row = (T*)p.qkv + (int64_t)r * p.row_stride;
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid * 8; i < nq + nk; i += 256 * 8) {
+        float v[8];
+        unpack8(*reinterpret_cast<const uint4*>(row + i), v);
+        const bool is_q = i < nq;
+        const float* b = is_q ? p.q_b : p.k_b;
+        if (b) {
+            float bb[8];
+            load8(b + (is_q ? i : i - nq), bb);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] += bb[j];
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc += v[j] * v[j];
+        if (is_q) sq += acc; else sk += acc;
+        *reinterpret_cast<float4*>(y + i) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(y + i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    sq = warp_sum(sq);
+    sk = warp_sum(sk);
+    if (lane == 0) part[warp] = sq, part[8 + warp] = sk;
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tq += part[w], tk += part[8 + w];
+    const float inv_q = p.q_w ? 1.0f / sqrtf(tq / (float)nq + p.eps) : 1.f;
+    const float inv_k = p.k_w && nk > 0 ? 1.0f / sqrtf(tk / (float)nk + p.eps) : 1.f;
+    const int pos = p.row_pos[r];
+    const int half = p.rot / 2;
+    const int tpos = (half == 0 || gb_check(pos, p.table_positions, GB_CHECK_ROPE_POSITION)) ? pos : 0;
+    const float* c = p.cos_t + (int64_t)tpos * half;
+    const float* s = p.sin_t + (int64_t)tpos * half;
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (p.write_kv && p.kv_heads > 0) {
+        const int slot = p.seq_slot[p.row_seq[r]];
+        const int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot, p.max_slots), pos, p.bt_stride, p.pages);
+        kdst = (T*)p.k_plane + (page * p.kv_heads * GB_PAGE + (pos % GB_PAGE)) * (int64_t)d;
+        vdst = (T*)p.v_plane + (page * p.kv_heads * GB_PAGE + (pos % GB_PAGE)) * (int64_t)dv;
+    }
+    const int n_rot = nq + (kdst ? nk : 0);
+    for (int i = tid * 8; i < n_rot; i += 256 * 8) {
+        const bool is_q = i < nq;
+        const float inv = is_q ? inv_q : inv_k;
+        const float* w = is_q ? p.q_w : p.k_w;
+        const int base = is_q ? 0 : nq;
+        const int e = (i - base) % d;
+        float n[8], v[8];
+        load8(y + i, n);
+        if (w) {
+            float ww[8];
+            load8(w + (i - base), ww);
+#pragma unroll
+            for (int j = 0; j < 8; j++) n[j] = n[j] * inv * ww[j];
+        }
+        if (e < p.rot) {
+            const bool low = e < half;
+            const int ip = low ? i + half : i - half;
+            float m[8], cc[8], ss[8];
+            load8(y + ip, m);
+            if (w) {
+                float ww[8];
+                load8(w + (ip - base), ww);
+#pragma unroll
+                for (int j = 0; j < 8; j++) m[j] = m[j] * inv * ww[j];
+            }
+            load8(c + (low ? e : e - half), cc);
+            load8(s + (low ? e : e - half), ss);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = low ? n[j] * cc[j] - m[j] * ss[j] : n[j] * cc[j] + m[j] * ss[j];
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] = n[j];
+        }
+        T* dst = is_q ? row + i : kdst + (int64_t)((i - nq) / d) * GB_PAGE * d + e;
+        *reinterpret_cast<uint4*>(dst) = pack8(v);
+    }
+    if (vdst) {
+        const T* vsrc = row + nq + nk;
+        for (int i = tid * 8; i < nv; i += 256 * 8) {
+            const int kvh = i / dv, e = i - kvh * dv;
+            float v[8];
+            unpack8(*reinterpret_cast<const uint4*>(vsrc + i), v);
+            if (p.v_b) {
+                float bb[8];
+                load8(p.v_b + i, bb);
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] += bb[j];
+            }
+            *reinterpret_cast<uint4*>(vdst + (int64_t)kvh * GB_PAGE * dv + e) = pack8(v);
+        }
+    }
+}
+
 // The common geometry (bfloat16, head_dim 128 rotated in full): a warp per head and ROPE_ROWS
 // consecutive rows, every lane holds four consecutive elements of each row, so element i and its
 // partner i + 64 sit in lanes l and l ^ 16.  All loads of the warp's rows (positions, elements,
@@ -725,9 +853,18 @@ GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* pp, int dtype, cudaSt
             if (span_smem > 48 * 1024) cudaFuncSetAttribute(qk_rope_span_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem);
             qk_rope_span_kernel<float><<<p.rows, 256, span_smem, stream>>>(p);
         } else {
-            if (span_smem > 48 * 1024)
-                cudaFuncSetAttribute(qk_rope_span_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem);
-            qk_rope_span_kernel<__nv_bfloat16><<<p.rows, 256, span_smem, stream>>>(p);
+            const int half = p.rot / 2;
+            const bool by_eight = !p.pairs && !(p.d & 7) && !(half & 7) && !((p.dv > 0 ? p.dv : p.d) & 7) && !(p.row_stride & 7) &&
+                                  !(((uintptr_t)p.qkv | (uintptr_t)p.q_b | (uintptr_t)p.k_b | (uintptr_t)p.v_b | (uintptr_t)p.q_w | (uintptr_t)p.k_w |
+                                     (uintptr_t)p.cos_t | (uintptr_t)p.sin_t | (uintptr_t)p.k_plane | (uintptr_t)p.v_plane) & 15);
+            if (by_eight) {
+                if (span_smem > 48 * 1024) cudaFuncSetAttribute(qk_rope_span_vec_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem);
+                qk_rope_span_vec_kernel<<<p.rows, 256, span_smem, stream>>>(p);
+            } else {
+                if (span_smem > 48 * 1024)
+                    cudaFuncSetAttribute(qk_rope_span_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)span_smem);
+                qk_rope_span_kernel<__nv_bfloat16><<<p.rows, 256, span_smem, stream>>>(p);
+            }
         }
         GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
         return 0;
