@@ -580,3 +580,25 @@ def test_trace_program_on_a_folder(models, tmp_path):
         close(read(1), wb[3:4], TOL[dtype], MOST[dtype])
         close(read(2), np.stack([wa[67], wb[4]]), TOL[dtype], MOST[dtype])
         close(read(3), wa[69:70], TOL[dtype], MOST[dtype])
+
+
+def test_the_command_line_writes_and_runs_a_named_configuration(tmp_path):
+    """-random-config NAME -write-model DIR, then -model DIR: the plain model reads the written folder
+    and would have chosen the same tokens."""
+    out = tmp_path / "written"
+    run = lambda *a: subprocess.run([sys.executable, "-m", "gophonic_b200", *a], cwd=ROOT, capture_output=True, text=True, timeout=600)
+    r = run("-random-config", "kalonex-tiny", "-weights-seed", "4", "-write-model", str(out))
+    assert r.returncode == 0, r.stderr[-2000:]
+    cfg, w = P.read_model(str(out))
+    assert cfg["architecture"] == "Kalonex" and {n: tuple(a.shape) for n, a in w.items()} == P.tensor_shapes(cfg)
+    r = run("-model", str(out), "-format", "f32", "-max-tokens", "6", "3,9,27", "100")
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [l["prompt"] for l in lines] == [[3, 9, 27], [100]]
+    for l in lines:
+        ids = list(l["prompt"])
+        assert len(l["tokens"]) == 6
+        for t in l["tokens"]:
+            logits = P.forward(cfg, w, ids)[-1]
+            assert logits.max() - logits[t] <= 1e-5
+            ids.append(t)
