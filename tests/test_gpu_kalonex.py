@@ -490,7 +490,7 @@ def test_mixture_rows(rows, sizes, dtype):
 
 @pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(5, 72, 40, [0, 3, 130, 0, 257]), (3, 300, 64, [1, 128, 129]), (7, 128, 200, [40, 0, 0, 9, 300, 64, 2]),
-                                   (1, 8, 8, [5]), (4, 520, 136, [127, 1, 256, 70])])
+                                   (1, 8, 8, [5]), (4, 520, 152, [127, 1, 256, 70])])
 def test_products_of_groups_of_rows_in_one_launch(shape, out_dtype):
     """Rows sorted by group, every group times its own block of the weights (blocks of rows, gated blocks with a
     weight a row, blocks of columns, rows written through a map), against one float64 product a group.  Groups that
