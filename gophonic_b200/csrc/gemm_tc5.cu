@@ -336,7 +336,7 @@ template <typename TC>
 __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                const __grid_constant__ CUtensorMap map_c, TC* __restrict__ C, int M, int N,
-                                                               int K, int64_t ldc, int epi) {
+                                                               int K, int64_t ldc, int epi, const float* __restrict__ bias) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* staging = tiles + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES;  // [4 epilogue warps][2][32 x 32 floats]
@@ -472,6 +472,24 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
                 if (n0 + c0 >= N) break;  // uniform across the warp
                 uint32_t r[32];
                 tmem_ld32(t_addr + (uint32_t)c0, r);
+                if (bias != nullptr) {
+                    // a vector over the columns (a projection's bias) joins the float32 sums before any epilogue
+                    const int cb = n0 + c0;
+                    if (cb + 32 <= N && (((uintptr_t)bias & 15) == 0)) {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            const float4 b = __ldg(reinterpret_cast<const float4*>(bias + cb) + e);
+                            r[e * 4] = __float_as_uint(__uint_as_float(r[e * 4]) + b.x);
+                            r[e * 4 + 1] = __float_as_uint(__uint_as_float(r[e * 4 + 1]) + b.y);
+                            r[e * 4 + 2] = __float_as_uint(__uint_as_float(r[e * 4 + 2]) + b.z);
+                            r[e * 4 + 3] = __float_as_uint(__uint_as_float(r[e * 4 + 3]) + b.w);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (cb + j < N) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(bias + cb + j));
+                    }
+                }
                 if (epi == 2) {
                     // C += tile: the warp lays its 32 x 32 floats out in shared memory (128-byte rows,
                     // 16-byte pieces swizzled as the tensor map says) and one lane hands them to a TMA
@@ -513,7 +531,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_pair_kernel(const __grid_con
 }
 
 template <typename TC>
-int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int epi, cudaStream_t stream) {
+int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldw, int64_t ldc, int epi, cudaStream_t stream,
+                const float* bias = nullptr) {
     const int smem = PAIR_STAGES * PAIR_STAGE_BYTES + PAIR_STAGING_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -548,7 +567,7 @@ int launch_pair(const void* A, const void* W, void* C, int M, int N, int K, int6
     if (total > 0x7fffffff) GB_REFUSE("gemm_tc5_pair: %lld tiles are too many", (long long)total);
     const int pairs = total < sms / 2 ? (int)total : sms / 2;  // one pair of CTAs per pair of SMs walks the tiles
     cudaError_t e = launch_pdl_cluster(gemm_tc5_pair_kernel<TC>, dim3(2 * pairs), dim3(THREADS), (size_t)smem, stream, 2, 1, map_a, map_w,
-                                       map_c, (TC*)C, M, N, K, ldc, epi);
+                                       map_c, (TC*)C, M, N, K, ldc, epi, bias);
     if (e != cudaSuccess) GB_REFUSE("gemm_tc5_pair: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -836,8 +855,9 @@ int launch_grouped(const void* A, const void* W, void* C, const int* offsets, in
 }  // namespace
 
 static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, int epi, int pair,
-               cudaStream_t stream, int64_t ldw = 0) {
+               cudaStream_t stream, int64_t ldw = 0, const float* bias = nullptr) {
     if (M <= 0 || N <= 0) return 0;
+    if (bias != nullptr && !pair) GB_REFUSE("gemm_tc5: a vector over the columns is added by the paired kernel only");
     if (ldw == 0) ldw = K;
     if ((ldw & 7) || ldw < K) GB_REFUSE("gemm_tc5: row stride %lld of W must be a multiple of 8 and at least K", (long long)ldw);
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5: K = %d must be a positive multiple of 8", K);
@@ -847,8 +867,8 @@ static int tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N,
     if (epi == 1 && ((N & 15) || ldc < N / 2)) GB_REFUSE("gemm_tc5: the SwiGLU epilogue needs N = %d to be a multiple of 16", N);
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5: operands must be 16-byte aligned");
     if (pair) {
-        if (c_dtype == GB_F32) return launch_pair<float>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
-        if (c_dtype == GB_BF16) return launch_pair<__nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
+        if (c_dtype == GB_F32) return launch_pair<float>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream, bias);
+        if (c_dtype == GB_BF16) return launch_pair<__nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream, bias);
     } else {
         if (c_dtype == GB_F32) return launch<float>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
         if (c_dtype == GB_BF16) return launch<__nv_bfloat16>(A, W, C, M, N, K, lda, ldw, ldc, epi, stream);
@@ -881,6 +901,12 @@ GB_API int gb_gemm_tc5_pair_swiglu(const void* A, const void* W, void* C, int c_
 // C[M, N] += A W^T for a float32 C (the residual stream), on the paired-SM kernel.
 GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream) {
     return tc5(A, W, C, GB_F32, M, N, K, lda, ldc, 2, 1, stream);
+}
+
+// C[M, N] = A W^T + bias (add 0) or C[M, N] += A W^T + bias (add 1, float32 C), bias[N] float32, on the paired-SM kernel.
+GB_API int gb_gemm_tc5_pair_bias(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, int add,
+                                 const float* bias, cudaStream_t stream) {
+    return tc5(A, W, C, c_dtype, M, N, K, lda, ldc, add ? 2 : 0, 1, stream, 0, bias);
 }
 
 // C[M, N / 2] = silu(A Wg^T) * (A Wu^T); W holds gate and up rows interleaved in blocks of eight.

@@ -237,9 +237,9 @@ def gemm_add_accepts(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> boo
             and out.stride(0) % 4 == 0 and out.data_ptr() % 16 == 0)
 
 
-def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
-    """out += a @ w^T in the epilogue of the tiled tcgen05 kernel (``out`` float32: the residual
-    stream); the sum per element is out + product, both float32, as a separate add would give."""
+def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+    """out += a @ w^T (+ ``bias``, a float32 vector over the columns) in the epilogue of the tiled tcgen05 kernel
+    (``out`` float32: the residual stream); the sum per element is out + (product + bias), all float32."""
     _need(a, "gemm a", torch.bfloat16, 2, contiguous=False)
     _need(w, "gemm w", torch.bfloat16, 2)
     _need(out, "gemm out", torch.float32, 2, contiguous=False)
@@ -247,6 +247,13 @@ def gemm_add(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (M, N) or a.stride(1) != 1 or out.stride(1) != 1 or not gemm_add_accepts(a, w, out):
         raise KernelError(f"gemm_add: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32, 1)
+        if bias.numel() != N:
+            raise KernelError(f"gemm_add: a bias of {bias.numel()} for {N} columns")
+        _check(_lib.gb_gemm_tc5_pair_bias(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                          c_int64(a.stride(0)), c_int64(out.stride(0)), c_int(1), _ptr(bias), _stream()))
+        return
     _check(_lib.gb_gemm_tc5_pair_add(_ptr(a), _ptr(w), _ptr(out), c_int(M), c_int(N), c_int(K), c_int64(a.stride(0)),
                                      c_int64(out.stride(0)), _stream()))
 
@@ -388,8 +395,10 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
                              c_int64(out.stride(0)), _stream()))
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto") -> str:
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto", bias: Optional[torch.Tensor] = None) -> str:
     """out = a @ w^T, choosing the kernel by operand types and sizes.  Returns the kernel's name.
+    ``bias`` (a float32 vector over the columns, for a float32 ``out``) is added to the float32 sums: in the
+    epilogue of the paired tcgen05 kernel, by a row-wise kernel behind every other one.
 
     bfloat16 activations with bfloat16 weights go to the tensor-core kernels (``gemm_algo``): up to
     8 rows the fragment-streaming kernel, up to 64 rows (128 or 256 for narrow outputs) the tcgen05
@@ -407,6 +416,20 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     if out.dtype not in (torch.float32, torch.bfloat16):
         raise KernelError(f"gemm: output dtype {out.dtype}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32, 1)
+        if bias.numel() != N or out.dtype != torch.float32:
+            raise KernelError(f"gemm: a bias of {bias.numel()} for {N} columns of {out.dtype}")
+        fused = (algo in ("auto", "tc5_pair") and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
+                 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()
+                 and (algo == "tc5_pair" or gemm_algo(M, N, K) == "tc5_pair"))
+        if fused:
+            _check(_lib.gb_gemm_tc5_pair_bias(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                              c_int64(a.stride(0)), c_int64(out.stride(0)), c_int(0), _ptr(bias), _stream()))
+            return "tc5_pair"
+        name = gemm(a, w, out, algo)
+        add_bias(out, bias)
+        return name
     if algo == "simt" or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         gemm_simt(a, w, out)
         return "simt"

@@ -108,14 +108,10 @@ class GatedAttention(Attention):
                 and self.spec.hidden % 4 == 0 and ops.gemm_algo(rows, self.spec.hidden, self.o_dim) == "tc5_pair")
 
     def forward_into(self, batch, x: torch.Tensor, h: torch.Tensor, cache) -> None:
-        self.rt.ops.gemm_add(self._gated_heads(batch, x, cache), self.o, h)
-        if self.o_bias is not None:
-            self.rt.ops.add_bias(h, self.o_bias)
+        self.rt.ops.gemm_add(self._gated_heads(batch, x, cache), self.o, h, bias=self.o_bias)
 
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor, cache) -> None:
-        self.rt.ops.gemm(self._gated_heads(batch, x, cache), self.o, out)
-        if self.o_bias is not None:
-            self.rt.ops.add_bias(out, self.o_bias)
+        self.rt.ops.gemm(self._gated_heads(batch, x, cache), self.o, out, bias=self.o_bias)
 
     def folds_norm(self, rows: int, norm) -> bool:
         return False

@@ -4,7 +4,8 @@ with the embedding output and the pass's own vector is added,
     x <- W [x; x0] + steps[index].
 
 One row-wise kernel lays the residual (with whatever addend is still owed to it) and x0 side by side in the
-activation dtype, one product makes the new float32 residual, one row-wise kernel adds the vector.  The old
+activation dtype, one product makes the new float32 residual and adds the vector (in its epilogue for prompt-sized
+steps, by a row-wise kernel otherwise).  The old
 residual is not needed afterwards.  A junction is built once per schedule position that names it; positions that
 name the same tensors share them.
 """
@@ -45,6 +46,5 @@ class Reinject(Part):
         joined = torch.empty((rows, 2 * hidden), dtype=self.rt.act_dtype, device=h.device)
         ops.concat_cast(h, pending if isinstance(pending, torch.Tensor) else None, x0, joined)
         out = torch.empty((rows, hidden), dtype=torch.float32, device=h.device)
-        ops.gemm(joined, self.weight, out)
-        ops.add_bias(out, self.step)
+        ops.gemm(joined, self.weight, out, bias=self.step)
         return out

@@ -281,6 +281,33 @@ def test_gemm_adds_into_the_residual(ops, M, N, K):
     assert not ops.gemm_add_accepts(small, w, torch.empty((8, N), device=DEV))
 
 
+@pytest.mark.parametrize("M,N,K", [(192, 96, 64), (300, 1000, 512), (515, 520, 1032), (257, 296, 136), (8, 200, 64), (40, 72, 96)])
+def test_gemm_with_a_vector_over_the_columns(ops, M, N, K):
+    """out = a w^T + bias and out += a w^T + bias: the bias joins the float32 sums in the paired kernel's epilogue
+    (whole and ragged blocks of 32 columns), and follows as a row-wise kernel behind every other product."""
+    a, w = rnd(M, K, dtype=torch.bfloat16, seed=1), rnd(N, K, dtype=torch.bfloat16, scale=0.1, seed=2)
+    bias = rnd(N, seed=5)
+    want = a.double() @ w.double().T + bias.double()
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device=DEV)
+    name = ops.gemm(a, w, out, bias=bias)
+    assert ops.tc5_status() == 0
+    assert name == ops.gemm_algo(M, N, K)
+    close(out, want, 2e-5)
+    plain = torch.empty((M, N), dtype=torch.float32, device=DEV)
+    ops.gemm(a, w, plain)
+    assert torch.equal(out, plain + bias)
+    a32, w32 = a.float(), w.float()
+    ops.gemm(a32, w32, out, bias=bias)
+    close(out, want, 2e-5)
+    if ops.gemm_add_accepts(a, w, out):
+        h = rnd(M, N, seed=3)
+        ops.gemm_add(a, w, h, bias=bias)
+        assert ops.tc5_status() == 0
+        assert torch.equal(h, rnd(M, N, seed=3) + (plain + bias))
+    with pytest.raises(ops.KernelError):
+        ops.gemm(a, w, out, bias=bias[:-1].contiguous())
+
+
 # Sizes of a full-size layer: every CTA of the persistent kernels computes several tiles one after
 # the other (768 tiles of 256 x 256 on 74 pairs, 1536 of 128 x 256 on 148 CTAs), so both tensor-memory
 # accumulators are handed back more than once, the stage ring runs on across tiles and the staging
