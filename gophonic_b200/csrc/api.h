@@ -138,6 +138,8 @@ GB_API int gb_concat_cast(const float* h, const float* delta, const float* side,
 GB_API int gb_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int M, int N, int K, int64_t lda,
                         int64_t ldw, int64_t ldc, cudaStream_t stream);
 GB_API int gb_gemm_skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, cudaStream_t stream);
+GB_API int gb_gemm_skinny_bias(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
+                               const float* bias, cudaStream_t stream);
 GB_API int gb_gemm_skinny_swiglu(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
                                  cudaStream_t stream);
 GB_API int gb_gemm_tc5(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream);

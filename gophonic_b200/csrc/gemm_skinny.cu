@@ -18,7 +18,7 @@ constexpr int MIN_STEPS = 4;  // fewest 32-wide K steps a warp should own
 template <int MT>  // MT tiles of 8 batch rows
 __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                                                          void* __restrict__ Yv, int y_is_bf16, int M, int N, int K, int64_t ldx,
-                                                         int64_t ldy, int k_per_warp, int epi) {
+                                                         int64_t ldy, int k_per_warp, int epi, const float* __restrict__ bias) {
     extern __shared__ float red[];  // [KW][16][MT * 8]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, KW = blockDim.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
         if (b >= M || n0 + i >= N) continue;
         float s = 0.f;
         for (int w = 0; w < KW; w++) s += red[(size_t)w * 16 * MB + i * MB + b];
+        if (bias != nullptr) s += __ldg(bias + n0 + i);  // a vector over the columns joins the float32 sum
         if (y_is_bf16)
             ((__nv_bfloat16*)Yv)[(int64_t)b * ldy + n0 + i] = __float2bfloat16_rn(s);
         else
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__(512) gemm_skinny_kernel(const __nv_bfloat16* _
 
 template <int MT>
 int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, int epi,
-           cudaStream_t stream) {
+           cudaStream_t stream, const float* bias) {
     int steps = ceil_div(K, 32);
     // Few weight tiles (narrow outputs) leave SMs short of loads in flight: give each CTA more warps.
     // See skinny_warps() in mma.cuh.
@@ -158,7 +159,7 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
     // kernel ahead of it; see skinny_dependent() for when it is one
     const bool dependent = skinny_dependent(ceil_div(N, 16));
     cudaError_t e = launch_maybe_pdl(dependent, gemm_skinny_kernel<MT>, dim3(ceil_div(N, 16)), dim3(kw * 32), smem, stream, (const __nv_bfloat16*)X,
-                               (const __nv_bfloat16*)W, Y, (int)(c_dtype == GB_BF16), M, N, K, ldx, ldy, k_per_warp, epi);
+                               (const __nv_bfloat16*)W, Y, (int)(c_dtype == GB_BF16), M, N, K, ldx, ldy, k_per_warp, epi, bias);
     if (e != cudaSuccess) GB_REFUSE("gemm_skinny: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -166,7 +167,8 @@ int launch(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int
 }  // namespace
 
 static int skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy, int epi,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const float* bias = nullptr) {
+    if (bias != nullptr && epi != 0) GB_REFUSE("gemm_skinny: a vector over the columns goes with the plain epilogue only");
     if (M <= 0 || N <= 0) return 0;
     if (M > 64) GB_REFUSE("gemm_skinny: %d rows; this kernel takes at most 64", M);
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_skinny: K = %d must be a positive multiple of 8", K);
@@ -176,15 +178,21 @@ static int skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int
         GB_REFUSE("gemm_skinny: the SwiGLU epilogue needs N = %d to be a multiple of 16 and Y rows of at least N / 2 (stride %lld)", N, (long long)ldy);
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (c_dtype != GB_F32 && c_dtype != GB_BF16) GB_REFUSE("gemm_skinny: unknown output dtype %d", c_dtype);
-    if (M <= 8) return launch<1>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
-    if (M <= 16) return launch<2>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
-    if (M <= 32) return launch<4>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
-    return launch<8>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream);
+    if (M <= 8) return launch<1>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream, bias);
+    if (M <= 16) return launch<2>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream, bias);
+    if (M <= 32) return launch<4>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream, bias);
+    return launch<8>(X, W, Y, c_dtype, M, N, K, ldx, ldy, epi, stream, bias);
 }
 
 GB_API int gb_gemm_skinny(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
                           cudaStream_t stream) {
     return skinny(X, W, Y, c_dtype, M, N, K, ldx, ldy, 0, stream);
+}
+
+// Y = X W^T + bias, bias[N] float32.
+GB_API int gb_gemm_skinny_bias(const void* X, const void* W, void* Y, int c_dtype, int M, int N, int K, int64_t ldx, int64_t ldy,
+                               const float* bias, cudaStream_t stream) {
+    return skinny(X, W, Y, c_dtype, M, N, K, ldx, ldy, 0, stream, bias);
 }
 
 // Y[M, N / 2] = silu(X Wg^T) * (X Wu^T) where W holds gate and up rows interleaved in blocks of

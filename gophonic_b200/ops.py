@@ -398,7 +398,7 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto", bias: Optional[torch.Tensor] = None) -> str:
     """out = a @ w^T, choosing the kernel by operand types and sizes.  Returns the kernel's name.
     ``bias`` (a float32 vector over the columns, for a float32 ``out``) is added to the float32 sums: in the
-    epilogue of the paired tcgen05 kernel, by a row-wise kernel behind every other one.
+    epilogue of the paired tcgen05 kernel and of the few-row kernel, by a row-wise kernel behind every other one.
 
     bfloat16 activations with bfloat16 weights go to the tensor-core kernels (``gemm_algo``): up to
     8 rows the fragment-streaming kernel, up to 64 rows (128 or 256 for narrow outputs) the tcgen05
@@ -420,13 +420,18 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, algo: str = "auto"
         _need(bias, "gemm bias", torch.float32, 1)
         if bias.numel() != N or out.dtype != torch.float32:
             raise KernelError(f"gemm: a bias of {bias.numel()} for {N} columns of {out.dtype}")
-        fused = (algo in ("auto", "tc5_pair") and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
-                 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()
-                 and (algo == "tc5_pair" or gemm_algo(M, N, K) == "tc5_pair"))
-        if fused:
+        fused = ""
+        if (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and a.stride(0) % 8 == 0
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()):
+            fused = gemm_algo(M, N, K) if algo == "auto" else algo
+        if fused == "tc5_pair":
             _check(_lib.gb_gemm_tc5_pair_bias(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
                                               c_int64(a.stride(0)), c_int64(out.stride(0)), c_int(0), _ptr(bias), _stream()))
-            return "tc5_pair"
+            return fused
+        if fused == "skinny":
+            _check(_lib.gb_gemm_skinny_bias(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), c_int(M), c_int(N), c_int(K),
+                                            c_int64(a.stride(0)), c_int64(out.stride(0)), _ptr(bias), _stream()))
+            return fused
         name = gemm(a, w, out, algo)
         add_bias(out, bias)
         return name

@@ -281,7 +281,7 @@ def test_gemm_adds_into_the_residual(ops, M, N, K):
     assert not ops.gemm_add_accepts(small, w, torch.empty((8, N), device=DEV))
 
 
-@pytest.mark.parametrize("M,N,K", [(192, 96, 64), (300, 1000, 512), (515, 520, 1032), (257, 296, 136), (8, 200, 64), (40, 72, 96)])
+@pytest.mark.parametrize("M,N,K", [(192, 96, 64), (300, 1000, 512), (515, 520, 1032), (257, 296, 136), (8, 200, 64), (3, 1000, 2048), (1, 24, 40), (40, 72, 96)])
 def test_gemm_with_a_vector_over_the_columns(ops, M, N, K):
     """out = a w^T + bias and out += a w^T + bias: the bias joins the float32 sums in the paired kernel's epilogue
     (whole and ragged blocks of 32 columns), and follows as a row-wise kernel behind every other product."""
