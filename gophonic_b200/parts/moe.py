@@ -77,6 +77,9 @@ class MoE(FeedForward):
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
         self._experts(batch, x, out)
         if self.shared is not None:
+            if out.dtype == torch.float32 and self.shared.adds_in_place(x.shape[0]):
+                self.shared.forward_into(batch, x, out)     # its last product adds into the experts' sum
+                return
             both = torch.empty_like(out)
             self.shared.forward(batch, x, both)
             self.rt.ops.add_rows(out, both)
