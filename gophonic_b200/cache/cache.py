@@ -166,7 +166,13 @@ class Cache:
             if isinstance(req, KVRequest):
                 # values as wide as keys: the key every such group has always had; else the width is part of it
                 key = (req.kv_heads, req.head_dim, req.window)
-                if req.value_dim and req.value_dim != req.head_dim:
+                vheads, in_keys = int(getattr(req, "value_heads", 0) or 0), bool(getattr(req, "values_in_keys", False))
+                if (vheads and vheads != req.kv_heads) or in_keys:
+                    # value heads of their own count, or values that are channels of the keys: the whole geometry is the key
+                    if in_keys and (vheads not in (0, req.kv_heads) or (req.value_dim or req.head_dim) > req.head_dim):
+                        raise CacheError(f"schedule position {pos}: values inside the keys need as many value heads, no wider than the keys")
+                    key += (req.value_dim or req.head_dim, vheads or req.kv_heads, in_keys)
+                elif req.value_dim and req.value_dim != req.head_dim:
                     key += (req.value_dim,)
                 planes = self._kv_groups.setdefault(key, [])
                 self._plane[pos] = ("kv", key, len(planes))
@@ -184,15 +190,25 @@ class Cache:
         self._k: Dict[Tuple[int, ...], torch.Tensor] = {}
         self._v: Dict[Tuple[int, ...], torch.Tensor] = {}
         for key, planes in self._kv_groups.items():
-            kvh, d, dv = key[0], key[1], key[-1] if len(key) == 4 else key[1]
+            kvh, d, _, dv, vh, in_keys = self._geometry(key)
             self._k[key] = torch.zeros((len(planes), self.n_pages + 1, kvh, PAGE, d), dtype=dtype, device=self.device)
-            self._v[key] = torch.zeros((len(planes), self.n_pages + 1, kvh, PAGE, dv), dtype=dtype, device=self.device)
+            if in_keys:
+                self._v[key] = self._k[key][..., :dv]      # a view: the first channels of every key
+            else:
+                self._v[key] = torch.zeros((len(planes), self.n_pages + 1, vh, PAGE, dv), dtype=dtype, device=self.device)
         self._state: Dict[Tuple[Tuple[int, ...], torch.dtype], torch.Tensor] = {}
         for key, planes in self._state_groups.items():
             shape, sdtype = key
             self._state[key] = torch.zeros((len(planes), self.max_slots + 1) + tuple(shape), dtype=sdtype, device=self.device)
         self._ops = None
         self._stager = None
+
+    @staticmethod
+    def _geometry(key) -> Tuple[int, int, int, int, int, bool]:
+        """(kv heads, key size, window, value size, value heads, values inside the keys) of a key/value group."""
+        if len(key) == 6:
+            return key
+        return key[0], key[1], key[2], key[3] if len(key) == 4 else key[1], key[0], False
 
     def attach(self, ops, stager) -> None:
         """Use the kernel library (``block_table_set``, ``zero_pages``) and a pinned upload ring
@@ -203,9 +219,11 @@ class Cache:
     def groups(self) -> List[dict]:
         out = []
         for key, planes in self._kv_groups.items():
-            kvh, d, w, dv = key[0], key[1], key[2], key[-1] if len(key) == 4 else key[1]
+            kvh, d, w, dv, vh, in_keys = self._geometry(key)
+            per_token = kvh * d + (0 if in_keys else vh * dv)
             out.append({"kind": "kv", "kv_heads": kvh, "head_dim": d, "value_dim": dv, "window": w, "planes": list(planes),
-                        "bytes_per_token": len(planes) * kvh * (d + dv) * torch.empty((), dtype=self.dtype).element_size()})
+                        "value_heads": vh, "values_in_keys": in_keys,
+                        "bytes_per_token": len(planes) * per_token * torch.empty((), dtype=self.dtype).element_size()})
         for (shape, sdtype), planes in self._state_groups.items():
             out.append({"kind": "state", "shape": shape, "dtype": str(sdtype), "planes": list(planes)})
         return out
@@ -305,7 +323,8 @@ class Cache:
             self._ops.block_table_set(self.block_table, dev, n)
             for key in self._k:
                 self._ops.zero_pages(self._k[key], dev, n)
-                self._ops.zero_pages(self._v[key], dev, n)
+                if self._v[key].is_contiguous():      # a value plane that is a view of the keys was cleared with them
+                    self._ops.zero_pages(self._v[key], dev, n)
             return
         t = torch.tensor(triples, dtype=torch.int64).view(n, 3).to(self.device)
         self.block_table[t[:, 0], t[:, 1]] = t[:, 2].to(torch.int32)

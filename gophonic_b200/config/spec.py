@@ -37,22 +37,29 @@ class RotarySpec:
 
     inv_freq_i = theta^(-2i/rotary_dim) (internal/qwen3lm/weights.go:681-688); element i pairs with
     i + rotary_dim/2 (internal/qwen3lm/kernels_scalar.go:73-80).
+
+    ``scaling`` = (factor, low, high, original) stretches the slow frequencies for contexts longer than
+    ``original`` positions: a frequency f whose wavelength 2 pi / f is longer than original / low becomes
+    f / factor, one whose wavelength is shorter than original / high stays, and in between
+    s = (original / wavelength - low) / (high - low) blends them as (1 - s) f / factor + s f.
     """
     head_dim: int
     rotary_dim: int
     theta: float
     kind: str = "rope"
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
 class PairRotarySpec:
     """Rotary embedding in which neighbouring channels turn together: channels 2i and 2i + 1 of a
     head, i < rotary_dim / 2, by the angle pos * theta^(-2i/rotary_dim); the channels from
-    ``rotary_dim`` on pass unchanged."""
+    ``rotary_dim`` on pass unchanged.  ``scaling`` as for ``RotarySpec``."""
     head_dim: int
     rotary_dim: int
     theta: float
     kind: str = "rope_pairs"
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -123,6 +130,65 @@ class GatedAttentionSpec:
                                           ("k_norm", "k.norm"), ("sink", "sink"))
     bias_suffix: str = ".b"
     kind: str = "gated_attention"
+
+
+@dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Differential attention: every query head has two softmax maps over the same values and its output is the first
+    less ``lambda`` times the second.  q holds heads * 2 * head_dim rows and k kv_heads * 2 * head_dim, head by head
+    as [map 1, map 2]; v holds kv_heads * value_dim; query head h reads key/value head h // (heads / kv_heads).
+    Per head and map q and k are RMS-normed over ``head_dim`` (``qk_norm``, one weight of head_dim for q and one for k)
+    and then given the position encoding.  Scores (q . k) * scale over the keys j <= i that the mask leaves:
+    ``chunk`` > 0: only those in i's own block of ``chunk`` positions, counted from the sequence's start; ``window`` > 0:
+    only those with i - j < window.  With
+
+        lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + lambda_init        (four learned vectors of head_dim)
+
+    head h's output is o = a1 - lambda a2, o / sqrt(mean(o^2) + eps) * (1 - lambda_init), and the heads go
+    through the output projection.  ``names`` maps q, k, v, o, the two norms and the four vectors to tensor-name
+    suffixes under the mixer's prefix."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    position: object
+    lambda_init: float
+    eps: float
+    qk_norm: Optional[RMSNormSpec] = None
+    chunk: int = 0
+    window: int = 0
+    names: Tuple[Tuple[str, str], ...] = (("q", "q"), ("k", "k"), ("v", "v"), ("o", "o"), ("q_norm", "q.norm"), ("k_norm", "k.norm"),
+                                          ("lq1", "lq1"), ("lk1", "lk1"), ("lq2", "lq2"), ("lk2", "lk2"))
+    kind: str = "diff_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose queries, keys and values are made from low-rank latents.  With h the mixer's input:
+
+        c_q = rmsnorm(W_dq h) (q_rank, weight ``dq.norm``),   q = W_uq c_q: per head [head_dim plain | rot_dim rotated]
+        W_dkv h = [kv_rank | rot_dim]:  c = rmsnorm(first part) (weight ``dkv.norm``),  k_r = the rest, rotated, one for all heads
+        per head: k = [W_uk c | k_r],  v = W_uv c  (value_dim),   score = (q . k) * scale
+
+    Only c and k_r are cached.  ``position`` is the encoding of the rotated part (its ``head_dim`` is rot_dim);
+    ``window`` > 0: row i sees j with 0 <= i - j < window; ``chunk`` > 0: only its own block of positions."""
+    hidden: int
+    heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    position: object
+    eps: float
+    window: int = 0
+    chunk: int = 0
+    names: Tuple[Tuple[str, str], ...] = (("dq", "dq"), ("dq_norm", "dq.norm"), ("uq", "uq"), ("dkv", "dkv"), ("dkv_norm", "dkv.norm"),
+                                          ("uk", "uk"), ("uv", "uv"), ("o", "o"))
+    kind: str = "latent_attention"
 
 
 @dataclass(frozen=True)
@@ -224,7 +290,12 @@ class MoESpec:
     * ``renorm`` False: the chosen scores are the weights as they are;
     * ``weight_on`` "input": a weight multiplies its expert's input, out = sum expert(w x), not its output;
     * ``act`` "swiglu": an expert is down(silu(gate x) * (up x)) with a third matrix ``e<j>.gate``;
-    * ``shared``: a ``SwiGLUSpec`` of a further expert under ``shared_prefix`` that every token uses, with weight 1."""
+    * ``act`` "glu_clamp": the same three matrices, down(g sigmoid(act_slope g) (u + 1)) with g = min(gate x, act_limit)
+      and u = clamp(up x, -act_limit, act_limit);
+    * ``shared``: the spec of a further feed-forward under ``shared_prefix`` that every token uses, with weight 1, or
+      with ``shared_gate`` with weight sigmoid(w . x), w the tensor ``shared_prefix + shared_gate_name`` ([1, hidden]);
+    * ``router_bias``: the router's logits carry a bias (tensor ``router`` + ``router_bias_suffix``);
+    * ``renorm_eps`` 0 with ``score`` "softmax" and ``renorm``: the weights are the softmax over the chosen logits alone."""
     hidden: int
     experts: int
     top: int
@@ -237,6 +308,12 @@ class MoESpec:
     act: str = "relu2"
     shared: Optional[object] = None
     shared_prefix: str = "shared."
+    act_limit: float = 0.0
+    act_slope: float = 1.0
+    router_bias: bool = False
+    router_bias_suffix: str = ".b"
+    shared_gate: bool = False
+    shared_gate_name: str = "sg"
 
 
 @dataclass(frozen=True)
@@ -247,6 +324,26 @@ class SwiGLUSpec:
     intermediate: int
     kind: str = "swiglu"
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
+@dataclass(frozen=True)
+class ReluSquaredSpec:
+    """down(relu(up(x))^2).  ``names``: the tensors of the up and down projections under the part's prefix."""
+    hidden: int
+    intermediate: int
+    kind: str = "relu2_ff"
+    names: Tuple[str, str] = ("up", "down")
+
+
+@dataclass(frozen=True)
+class ClampedGLUSpec:
+    """down(g sigmoid(slope g) (u + 1)) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit)."""
+    hidden: int
+    intermediate: int
+    limit: float
+    slope: float
+    kind: str = "glu_clamp"
+    names: Tuple[str, str, str] = ("gate", "up", "down")
 
 
 @dataclass(frozen=True)
@@ -297,6 +394,28 @@ class HyperLayerSpec:
     mixer_norm_prefix: str = "norm1"
     feed_forward_norm_prefix: str = "norm2"
     connection_prefixes: Tuple[str, str] = ("hc1.", "hc2.")
+
+
+@dataclass(frozen=True)
+class PostNormLayerSpec:
+    """One layer whose sublayers read the residual itself and whose norms stand behind them:
+
+        x <- x + mult * scale_1 * norm_1(mixer(x));    x <- x + mult * scale_2 * norm_2(feed_forward(x))
+
+    ``scale_q``: a learned vector per sublayer (tensor ``prefix + scale_names[q]``; None: no such vector).
+    ``feed_forward`` and ``feed_forward_norm`` None: the layer is its mixer sublayer alone."""
+    prefix: str
+    mixer: object
+    feed_forward: object
+    mixer_norm: object
+    feed_forward_norm: object
+    residual_mult: float = 1.0
+    scale_names: Optional[Tuple[str, str]] = ("ls1", "ls2")
+    block: str = "postnorm"
+    mixer_prefix: str = "mix."
+    feed_forward_prefix: str = "mlp."
+    mixer_norm_prefix: str = "norm1"
+    feed_forward_norm_prefix: str = "norm2"
 
 
 @dataclass(frozen=True)

@@ -43,6 +43,10 @@ struct AttnParamsX : AttnParams {
     int keep_first;  // with a window: keys at positions below this stay visible however far back they lie
     int sink;        // 1: the softmax denominator carries one more term (a key without a value): exp(sinks[head]), or one unit
     const float* sinks;  // [heads] the sink's score per head, in the units of the scaled scores but not scaled itself; null: 0
+    int chunk;       // > 0: position i sees j <= i only inside its own block of `chunk` positions, counted from position 0 of the sequence
+    int v_share;     // > 1: this many consecutive key heads read one value head (the value plane holds kv_heads / v_share heads)
+    int64_t v_row_stride;  // elements between the values of two tokens of a page; 0: dv.  A value plane that is a view of the key
+                           // plane (the values are the first dv channels of the keys) has the keys' stride d.
 };
 
 // Per-head q/k RMSNorm, rotary embedding and cache write on the rows of a fused q|k|v buffer.
@@ -77,6 +81,7 @@ struct QkRopeParamsX : QkRopeParams {
     int pairs;         // 1: channels 2j and 2j + 1 turn together by angle j; 0: channels j and j + rot / 2
     int dv;            // size of a value head; 0: the same as d
     int span;          // 1: q is normed over all its heads together (q_w: [heads * d]) and k likewise (k_w: [kv_heads * d]); 0: per head
+    int v_share;       // > 1: the row holds kv_heads / v_share value heads (that many key heads read one value head); 0, 1: kv_heads
 };
 
 // A matrix state per (sequence, head), updated token by token: S <- diag(a) S + b k v^T, o = S^T q.
@@ -185,6 +190,8 @@ static inline AttnParamsX gb_attn_widen(const AttnParams& a) {
     static_cast<AttnParams&>(x) = a;
     x.dv = x.keep_first = x.sink = 0;
     x.sinks = nullptr;
+    x.chunk = x.v_share = 0;
+    x.v_row_stride = 0;
     return x;
 }
 
@@ -308,9 +315,12 @@ struct MoeRowsParams {
     int rows, experts, top, ff, hidden;
     int act_kind;           // 0: relu(up x)^2; 1: gated, silu(gate x) * (up x), `up` holding each expert's gate rows, then its up rows
     int weight_input;       // 1: a pair's weight multiplies its expert's input; 0: its output
+    float limit, slope;     // act_kind 2: g sigmoid(slope g) (v + 1) with g = min(gate x, limit), v = clamp(up x, -limit, limit)
 };
 GB_API int gb_moe_act_kind(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
                            int kind, int weight_input, int dtype, cudaStream_t stream);
+GB_API int gb_moe_act_clamped(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
+                              int kind, int weight_input, float limit, float slope, int dtype, cudaStream_t stream);
 GB_API int gb_moe_rows(const MoeRowsParams* p, int dtype, int w_dtype, cudaStream_t stream);
 GB_API int gb_moe_group_weights(const int* index, int rows, int top, int experts, int* offsets, int* place, int* src_row, const float* weight,
                                 float* sorted_weight, cudaStream_t stream);
@@ -321,3 +331,17 @@ GB_API int gb_moe_combine(const float* ys, const int* place, const float* weight
                           cudaStream_t stream);
 GB_API int gb_moe_rows_grouped(const MoeRowsParams* p, const int* offsets, const int* src_row, float* ys, int dtype, int w_dtype,
                                cudaStream_t stream);
+
+// Layers whose norm stands behind the sublayer, differential attention, latent attention (postnorm.cu).
+GB_API int gb_norm_scale_add(float* h, const float* y, const float* w, float eps, int rows, int n, void* x_out, int x_dtype, cudaStream_t stream);
+GB_API int gb_diff_combine(const void* ctx, int64_t ctx_stride, void* out, int64_t out_stride, int rows, int heads, int per_group, int dv,
+                           float lambda, float eps, float factor, int dtype, cudaStream_t stream);
+GB_API int gb_add_rows_gated(float* out, const float* y, const float* z, int64_t z_stride, int rows, int n, cudaStream_t stream);
+GB_API int gb_latent_prep(const void* lat, int64_t lat_stride, void* cq, const float* q_w, const float* kv_w, float eps, const float* cos_t,
+                          const float* sin_t, int table_positions, const int* row_pos, const int* row_seq, const int* seq_slot,
+                          const int* block_table, int bt_stride, void* k_plane, int write_kv, int rows, int q_rank, int kv_rank, int rot, int pages,
+                          int max_slots, int dtype, cudaStream_t stream);
+GB_API int gb_latent_q_rot(const void* q, int64_t q_stride, void* out, int64_t out_stride, int rows, int heads, int d, int rot, int out_head,
+                           const float* cos_t, const float* sin_t, int table_positions, const int* row_pos, int dtype, cudaStream_t stream);
+GB_API int gb_head_gemm(const void* a, int64_t a_row_stride, int64_t a_head_stride, const void* w, void* out, int64_t o_row_stride,
+                        int64_t o_head_stride, int rows, int heads, int K, int N, int dtype, int w_dtype, cudaStream_t stream);

@@ -19,12 +19,15 @@ namespace {
 constexpr int RW = 4;       // rows per warp
 constexpr int ROWS = 16;    // rows per CTA (4 warps)
 constexpr int KT = 32;      // keys per tile
+constexpr int SIMT_MAX_D = 640;    // widest key head (a latent of 512 and 128 rotated channels); what one CTA stages
+constexpr int SIMT_MAX_DV = 512;   // widest value head
 
 template <typename T, int NE>
 __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
     extern __shared__ float sm[];
     const int d = p.d, ks = d + 1;
     const int dv = p.dv > 0 ? p.dv : p.d, vs = dv + 1;   // values may be narrower or wider than keys
+    const int64_t v_tok = p.v_row_stride > 0 ? p.v_row_stride : dv;   // a value plane may be a view of wider rows
     float* Qs = sm;                // [16][d], pre-scaled
     float* Ks = Qs + ROWS * d;     // [32][d + 1]
     float* Vs = Ks + KT * ks;      // [32][dv + 1]
@@ -36,6 +39,8 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
 
     const int seq = blockIdx.z / p.num_splits, split = blockIdx.z % p.num_splits;
     const int kvh = blockIdx.y / hchunks, chunk = blockIdx.y % hchunks;
+    // consecutive key heads may read one value head: -1 if every key head has its own
+    const int v_heads = p.v_share > 1 ? p.kv_heads / p.v_share : p.kv_heads, vh = p.v_share > 1 ? kvh / p.v_share : -1;
     const int q_len = p.seq_q_len[seq], kv_len = p.seq_kv_len[seq];
     const int q0 = blockIdx.x * QT;
     if (q0 >= q_len) return;
@@ -76,6 +81,11 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
         lo_pos = past + q0 - p.window + 1;
         if (lo_pos < 0) lo_pos = 0;
     }
+    if (p.chunk > 0) {
+        // the block of the tile's first row begins no later than any other row's
+        const int b = (past + q0) - (past + q0) % p.chunk;
+        if (b > lo_pos) lo_pos = b;
+    }
     const int t_lo = lo_pos / KT, t_hi = hi_pos / KT + 1;
     // With kept first tokens the tiles visited are those of keys [0, keep_first) and then those of the
     // window, each once and in order of position: tile index i < n_first is tile i, the others follow
@@ -107,7 +117,7 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
                 int64_t page = page_of(bt, key, p.bt_stride, p.pages);
                 int64_t at = (page * p.kv_heads + kvh) * GB_PAGE + (key % GB_PAGE);
                 const T* kp = (const T*)p.k_plane + at * (int64_t)d;
-                const T* vp = (const T*)p.v_plane + at * (int64_t)dv;
+                const T* vp = (const T*)p.v_plane + (vh < 0 ? at : (page * v_heads + vh) * GB_PAGE + (key % GB_PAGE)) * v_tok;
                 for (int c = lane; c < d; c += 32) Ks[j * ks + c] = to_f32<T>(kp[c]);
                 for (int c = lane; c < dv; c += 32) Vs[j * vs + c] = to_f32<T>(vp[c]);
             } else {
@@ -131,7 +141,8 @@ __global__ void __launch_bounds__(128) attn_simt_kernel(AttnParamsX p) {
         float pr[RW];
 #pragma unroll
         for (int rr = 0; rr < RW; rr++) {
-            bool valid = row_ok[rr] && key <= row_pos[rr] && (p.window <= 0 || key > row_pos[rr] - p.window || key < p.keep_first);
+            bool valid = row_ok[rr] && key <= row_pos[rr] && (p.window <= 0 || key > row_pos[rr] - p.window || key < p.keep_first) &&
+                         (p.chunk <= 0 || key >= row_pos[rr] - row_pos[rr] % p.chunk);
             float sv = valid ? s[rr] : -INFINITY;
             float m_new = fmaxf(m[rr], warp_max(sv));
             if (m_new == -INFINITY) {
@@ -249,7 +260,7 @@ template <typename T, int NE>
 int launch_ne(const AttnParamsX& p, dim3 grid, size_t smem, cudaStream_t stream) {
     static bool configured = false;
     if (!configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_simt_kernel<T, NE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(attn_simt_kernel<T, NE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) GB_REFUSE("attention_simt: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = true;
     }
@@ -280,7 +291,9 @@ int launch(const AttnParamsX& p, cudaStream_t stream) {
         case 6: rc = launch_ne<T, 6>(p, grid, smem, stream); break;
         case 7: rc = launch_ne<T, 7>(p, grid, smem, stream); break;
         case 8: rc = launch_ne<T, 8>(p, grid, smem, stream); break;
-        default: GB_REFUSE("attention_simt: value size %d is larger than 256", dv);
+        case 9: case 10: case 11: case 12: rc = launch_ne<T, 12>(p, grid, smem, stream); break;
+        case 13: case 14: case 15: case 16: rc = launch_ne<T, 16>(p, grid, smem, stream); break;
+        default: GB_REFUSE("attention_simt: value size %d is larger than %d", dv, SIMT_MAX_DV);
     }
     if (rc) return rc;
     if (p.num_splits > 1) {
@@ -315,12 +328,15 @@ GB_API int gb_attention_simt_x(const AttnParamsX* pp, int dtype, cudaStream_t st
     AttnParamsX p = *pp;
     if (p.nseq <= 0 || p.max_q_len <= 0) return 0;
     if (p.heads <= 0 || p.kv_heads <= 0 || p.heads % p.kv_heads) GB_REFUSE("attention: %d heads over %d kv heads", p.heads, p.kv_heads);
-    if (p.d <= 0 || p.d > 256) GB_REFUSE("attention_simt: head_dim %d is outside [1, 256]", p.d);
+    if (p.d <= 0 || p.d > SIMT_MAX_D) GB_REFUSE("attention_simt: head_dim %d is outside [1, %d]", p.d, SIMT_MAX_D);
     if (p.num_splits < 1 || p.num_splits > MERGE_MAX_SPLITS) GB_REFUSE("attention: %d key splits; 1 to %d", p.num_splits, MERGE_MAX_SPLITS);
     if (p.num_splits > 1 && p.max_q_len != 1) GB_REFUSE("attention: key splits need single-token rows, got rows of up to %d", p.max_q_len);
     if (p.num_splits > 1 && !p.scratch) GB_REFUSE("attention: %d key splits without scratch memory", p.num_splits);
     if (p.window < 0) GB_REFUSE("attention: window %d", p.window);
-    if (p.dv < 0 || p.dv > 256) GB_REFUSE("attention_simt: value size %d is outside [1, 256]", p.dv);
+    if (p.dv < 0 || p.dv > SIMT_MAX_DV || (p.dv == 0 && p.d > SIMT_MAX_DV)) GB_REFUSE("attention_simt: value size %d is outside [1, %d]", p.dv ? p.dv : p.d, SIMT_MAX_DV);
+    if (p.chunk < 0) GB_REFUSE("attention: blocks of %d positions", p.chunk);
+    if (p.v_share < 0 || (p.v_share > 1 && p.kv_heads % p.v_share)) GB_REFUSE("attention: %d key heads share value heads by %d", p.kv_heads, p.v_share);
+    if (p.v_row_stride < 0 || (p.v_row_stride > 0 && p.v_row_stride < (p.dv ? p.dv : p.d))) GB_REFUSE("attention: value stride %lld", (long long)p.v_row_stride);
     if (p.keep_first < 0) GB_REFUSE("attention: %d kept first tokens", p.keep_first);
     if (dtype == GB_F32) return launch<float>(p, stream);
     if (dtype == GB_BF16) return launch<__nv_bfloat16>(p, stream);

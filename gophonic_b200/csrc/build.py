@@ -52,6 +52,7 @@ SOURCES = [
     "attention_sigmoid.cu",
     "hyper.cu",
     "moe.cu",
+    "postnorm.cu",
     "sampling.cu",
     "no_alloc.cu",
     "dispatch.cu",

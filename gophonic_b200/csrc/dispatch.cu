@@ -144,6 +144,7 @@ GB_API int gb_attention_algo(const AttnParams* p, int dtype) {
 GB_API int gb_attention_algo_x(const AttnParamsX* p, int dtype) {
     if (dtype != GB_BF16 || (p->d & 15) || !(p->d <= 128 || p->d == 256)) return GB_ATTN_SIMT;
     if (p->dv && p->dv != p->d) return GB_ATTN_SIMT;   // values of another size than keys: the CUDA-core kernel only
+    if (p->chunk > 0 || p->v_share > 1 || p->v_row_stride > 0) return GB_ATTN_SIMT;   // blocks of positions, shared or strided values
     if (p->max_q_len == 1) return GB_ATTN_DECODE_MMA;
     if (p->max_q_len >= TC5_ATTENTION_MIN_ROWS && p->d == 128 && !((uintptr_t)p->q & 15) && !(p->q_row_stride & 7) && !(p->out_row_stride & 7))
         return GB_ATTN_PREFILL_TC5;

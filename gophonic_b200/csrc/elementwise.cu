@@ -351,7 +351,8 @@ __global__ void qk_rope_kernel(QkRopeParamsX p) {
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int r = blockIdx.x;
     int head = blockIdx.y * 4 + warp;
-    int total_heads = p.heads + 2 * p.kv_heads;
+    const int v_heads = p.v_share > 1 ? p.kv_heads / p.v_share : p.kv_heads;   // key heads may share value heads
+    int total_heads = p.heads + p.kv_heads + v_heads;
     if (head >= total_heads) return;
     int d = p.d;
     const int dv = p.dv > 0 ? p.dv : d;
@@ -373,7 +374,7 @@ __global__ void qk_rope_kernel(QkRopeParamsX p) {
         int slot = p.seq_slot[p.row_seq[r]];
         int64_t page = page_of(block_table_row(p.block_table, p.bt_stride, slot, p.max_slots), pos, p.bt_stride, p.pages);
         T* plane = (T*)(is_k ? p.k_plane : p.v_plane);
-        dst = plane + ((page * p.kv_heads + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)(is_k ? d : dv);
+        dst = plane + ((page * (is_k ? p.kv_heads : v_heads) + kvh) * GB_PAGE + (pos % GB_PAGE)) * (int64_t)(is_k ? d : dv);
     }
     if (!is_q && !is_k) {  // value head: copy (plus its bias)
         if (bias)
@@ -831,7 +832,7 @@ GB_API int gb_qk_norm_rope_kv_write(const QkRopeParams* pp, int dtype, cudaStrea
     QkRopeParamsX x;
     static_cast<QkRopeParams&>(x) = *pp;
     x.q_b = x.k_b = x.v_b = nullptr;
-    x.pairs = x.dv = x.span = 0;
+    x.pairs = x.dv = x.span = x.v_share = 0;
     return gb_qk_norm_rope_kv_write_x(&x, dtype, stream);
 }
 
@@ -843,8 +844,10 @@ GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* pp, int dtype, cudaSt
     if (p.rot > 0 && (!p.cos_t || !p.sin_t)) GB_REFUSE("qk_norm_rope: rotary width %d without an angle table", p.rot);
     if (p.heads <= 0 || p.kv_heads < 0) GB_REFUSE("qk_norm_rope: heads %d, kv heads %d", p.heads, p.kv_heads);
     if (p.rows > 0x7fffffff / 2) GB_REFUSE("qk_norm_rope: %d rows are too many", p.rows);
-    int total_heads = p.heads + 2 * p.kv_heads;
+    if (p.v_share < 0 || (p.v_share > 1 && p.kv_heads % p.v_share)) GB_REFUSE("qk_norm_rope: %d key heads share value heads by %d", p.kv_heads, p.v_share);
+    int total_heads = p.heads + p.kv_heads + (p.v_share > 1 ? p.kv_heads / p.v_share : p.kv_heads);
     if (p.dv < 0 || p.dv > 1024) GB_REFUSE("qk_norm_rope: value size %d is outside [1, 1024]", p.dv);
+    if (p.span && p.v_share > 1) GB_REFUSE("qk_norm_rope: shared value heads with a norm over all heads are not built");
     if (p.span) {
         const size_t span_smem = ((size_t)(p.heads + p.kv_heads) * p.d + 16) * sizeof(float);
         if (span_smem > 200 * 1024) GB_REFUSE("qk_norm_rope: %d + %d heads of %d exceed what one CTA stages", p.heads, p.kv_heads, p.d);
@@ -869,7 +872,7 @@ GB_API int gb_qk_norm_rope_kv_write_x(const QkRopeParamsX* pp, int dtype, cudaSt
         GB_CHECK_LAUNCH("qk_norm_rope_kv_write");
         return 0;
     }
-    const bool plain = !p.q_b && !p.k_b && !p.v_b && !p.pairs && (p.dv == 0 || p.dv == p.d);
+    const bool plain = !p.q_b && !p.k_b && !p.v_b && !p.pairs && (p.dv == 0 || p.dv == p.d) && p.v_share <= 1;
     if (plain && dtype == GB_BF16 && p.d == 128 && p.rot == 128 && !(p.row_stride & 3) && !((uintptr_t)p.qkv & 7) &&
         !(((uintptr_t)p.q_w | (uintptr_t)p.k_w | (uintptr_t)p.cos_t | (uintptr_t)p.sin_t) & 15) && (p.q_w != nullptr) == (p.k_w != nullptr) &&
         ceil_div(total_heads, 8) <= 65535) {

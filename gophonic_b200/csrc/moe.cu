@@ -93,13 +93,17 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteParams p) {
 }
 
 // What an expert's hidden unit makes of its product(s) z (and, for a gated expert, u) and the pair's weight w:
-// kind 0: relu(z)^2; kind 1: silu(z) * u.  The weight multiplies the result, or (weight_input) the expert's
+// kind 0: relu(z)^2; kind 1: silu(z) * u; kind 2: g sigmoid(slope g) (v + 1) with g = min(z, limit) and
+// v = clamp(u, -limit, limit).  The weight multiplies the result, or (weight_input) the expert's
 // input, which for products without biases is the same as multiplying z and u.
-__device__ __forceinline__ float expert_act(float z, float u, float w, int kind, int weight_input) {
+__device__ __forceinline__ float expert_act(float z, float u, float w, int kind, int weight_input, float limit = 0.f, float slope = 1.f) {
     if (weight_input) z *= w, u *= w;
     float a;
     if (kind == 1) {
         a = z / (1.f + expf(-z)) * u;
+    } else if (kind == 2) {
+        const float g = fminf(z, limit), v = fminf(fmaxf(u, -limit), limit);
+        a = g / (1.f + expf(-slope * g)) * (v + 1.f);
     } else {
         const float r = fmaxf(z, 0.f);
         a = r * r;
@@ -110,7 +114,7 @@ __device__ __forceinline__ float expert_act(float z, float u, float w, int kind,
 // up: [rows, experts * (kind 1: 2 ff, gate rows then up rows of each expert; else ff)]; dense null: every weight is 1
 template <typename T>
 __global__ void moe_act_kernel(const T* __restrict__ up, int64_t up_stride, const float* __restrict__ dense, T* __restrict__ act,
-                               int64_t act_stride, int rows, int experts, int ff, int kind, int weight_input) {
+                               int64_t act_stride, int rows, int experts, int ff, int kind, int weight_input, float limit, float slope) {
     const int64_t n = (int64_t)experts * ff;
     const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * n) return;
@@ -118,13 +122,13 @@ __global__ void moe_act_kernel(const T* __restrict__ up, int64_t up_stride, cons
     const int64_t e = c / ff, i = c - e * ff;
     const float w = dense ? dense[r * experts + e] : 1.f;
     float z, u = 0.f;
-    if (kind == 1) {
+    if (kind != 0) {
         z = to_f32<T>(up[r * up_stride + e * 2 * ff + i]);
         u = to_f32<T>(up[r * up_stride + e * 2 * ff + ff + i]);
     } else {
         z = to_f32<T>(up[r * up_stride + c]);
     }
-    act[r * act_stride + c] = from_f32<T>(expert_act(z, u, w, kind, weight_input));
+    act[r * act_stride + c] = from_f32<T>(expert_act(z, u, w, kind, weight_input, limit, slope));
 }
 
 // a warp's share of the dot product of a weight row and a row of activations, 16 bytes a lane where both allow it
@@ -164,15 +168,15 @@ __global__ void __launch_bounds__(128) moe_up_rows_kernel(MoeRowsParams p) {
     if (i >= p.ff) return;
     const int r = pair / p.top;
     const int e = p.index[pair];
-    const int per = p.act_kind == 1 ? 2 : 1;      // a gated expert holds its gate rows, then its up rows
+    const int per = p.act_kind != 0 ? 2 : 1;      // a gated expert holds its gate rows, then its up rows
     const TW* w = (const TW*)p.up + ((int64_t)e * per * p.ff + i) * p.hidden;
     const T* x = (const T*)p.x + (int64_t)r * p.x_stride;
     const float a = warp_sum(warp_dot<T, TW>(w, x, p.hidden, lane));
-    const float b = p.act_kind == 1 ? warp_sum(warp_dot<T, TW>(w + (int64_t)p.ff * p.hidden, x, p.hidden, lane)) : 0.f;
+    const float b = p.act_kind != 0 ? warp_sum(warp_dot<T, TW>(w + (int64_t)p.ff * p.hidden, x, p.hidden, lane)) : 0.f;
     if (lane == 0) {
         // the same roundings as the stacked path: the product in the activation dtype, then the activation
         ((T*)p.act)[(int64_t)pair * p.ff + i] =
-            from_f32<T>(expert_act(to_f32<T>(from_f32<T>(a)), to_f32<T>(from_f32<T>(b)), p.weight[pair], p.act_kind, p.weight_input));
+            from_f32<T>(expert_act(to_f32<T>(from_f32<T>(a)), to_f32<T>(from_f32<T>(b)), p.weight[pair], p.act_kind, p.weight_input, p.limit, p.slope));
     }
 }
 
@@ -204,18 +208,18 @@ __global__ void __launch_bounds__(128) moe_up_grouped_kernel(MoeRowsParams p, co
     const int i = blockIdx.x * 4 + warp, e = blockIdx.y;
     const int lo = offsets[e], hi = offsets[e + 1];
     if (i >= p.ff || lo == hi) return;
-    const int per = p.act_kind == 1 ? 2 : 1;
+    const int per = p.act_kind != 0 ? 2 : 1;
     const TW* w = (const TW*)p.up + ((int64_t)e * per * p.ff + i) * p.hidden;
     for (int at = lo; at < hi; at++) {
         const T* x = (const T*)p.x + (int64_t)src_row[at] * p.x_stride;
         const float a = warp_sum(warp_dot<T, TW>(w, x, p.hidden, lane));
-        const float b = p.act_kind == 1 ? warp_sum(warp_dot<T, TW>(w + (int64_t)p.ff * p.hidden, x, p.hidden, lane)) : 0.f;
+        const float b = p.act_kind != 0 ? warp_sum(warp_dot<T, TW>(w + (int64_t)p.ff * p.hidden, x, p.hidden, lane)) : 0.f;
         if (lane == 0) {
             // a weight on the expert's input is applied here (p.weight: the pairs' weights in sorted order), one on its
             // output when the rows are added up
             const float pw = p.weight_input ? p.weight[at] : 1.f;
             ((T*)p.act)[(int64_t)at * p.ff + i] =
-                from_f32<T>(expert_act(to_f32<T>(from_f32<T>(a)), to_f32<T>(from_f32<T>(b)), pw, p.act_kind, p.weight_input));
+                from_f32<T>(expert_act(to_f32<T>(from_f32<T>(a)), to_f32<T>(from_f32<T>(b)), pw, p.act_kind, p.weight_input, p.limit, p.slope));
         }
     }
 }
@@ -368,16 +372,22 @@ GB_API int gb_moe_act(const void* up, int64_t up_stride, const float* dense, voi
 // weight_input 1: the weight multiplies the expert's input instead of its output.  dense null: weights of 1.
 GB_API int gb_moe_act_kind(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
                            int kind, int weight_input, int dtype, cudaStream_t stream) {
+    return gb_moe_act_clamped(up, up_stride, dense, act, act_stride, rows, experts, ff, kind, weight_input, 0.f, 1.f, dtype, stream);
+}
+
+// kind 2 as well: g sigmoid(slope g) (v + 1), g = min(gate, limit), v = clamp(up, -limit, limit), columns laid out as for kind 1.
+GB_API int gb_moe_act_clamped(const void* up, int64_t up_stride, const float* dense, void* act, int64_t act_stride, int rows, int experts, int ff,
+                              int kind, int weight_input, float limit, float slope, int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (experts <= 0 || ff <= 0) GB_REFUSE("moe_act: %d experts of %d", experts, ff);
-    if (kind != 0 && kind != 1) GB_REFUSE("moe_act: unknown activation %d", kind);
+    if (kind < 0 || kind > 2) GB_REFUSE("moe_act: unknown activation %d", kind);
     const int64_t total = (int64_t)rows * experts * ff;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == GB_F32)
-        moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)up, up_stride, dense, (float*)act, act_stride, rows, experts, ff, kind, weight_input);
+        moe_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)up, up_stride, dense, (float*)act, act_stride, rows, experts, ff, kind, weight_input, limit, slope);
     else if (dtype == GB_BF16)
         moe_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)up, up_stride, dense, (__nv_bfloat16*)act, act_stride,
-                                                                  rows, experts, ff, kind, weight_input);
+                                                                  rows, experts, ff, kind, weight_input, limit, slope);
     else
         GB_REFUSE("moe_act: unknown dtype %d", dtype);
     GB_CHECK_LAUNCH("moe_act");

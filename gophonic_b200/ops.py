@@ -521,7 +521,7 @@ def checked_status():
     found out of bounds since the last call (the access was skipped or redirected, nothing faulted).
     Always None in the ordinary build, whose kernels carry no checks.  Synchronises."""
     out = (c_int * 4)()
-    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid", "hyper"):
+    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid", "hyper", "postnorm"):
         code = int(getattr(_lib, "gb_checked_status_" + name)(out))
         if code or out[3]:
             return name, _CHECK_NAMES.get(code, f"code {code}"), out[1], out[2], out[3]
@@ -545,7 +545,7 @@ class _QkRopeParams(Structure):
         ("bt_stride", c_int), ("k_plane", c_void_p), ("v_plane", c_void_p),
         ("write_kv", c_int), ("rows", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("pages", c_int), ("max_slots", c_int),
-        ("q_b", c_void_p), ("k_b", c_void_p), ("v_b", c_void_p), ("pairs", c_int), ("dv", c_int), ("span", c_int),
+        ("q_b", c_void_p), ("k_b", c_void_p), ("v_b", c_void_p), ("pairs", c_int), ("dv", c_int), ("span", c_int), ("v_share", c_int),
     ]
 
 
@@ -555,21 +555,26 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                  row_pos: torch.Tensor, row_seq: torch.Tensor, seq_slot: torch.Tensor,
                  block_table: torch.Tensor,
                  k_plane: Optional[torch.Tensor], v_plane: Optional[torch.Tensor], write_kv: bool,
-                 biases=None, pairs: bool = False, value_dim: Optional[int] = None, span: bool = False) -> "_QkRopeParams":
+                 biases=None, pairs: bool = False, value_dim: Optional[int] = None, span: bool = False, v_share: int = 1) -> "_QkRopeParams":
     """``biases`` = (q, k, v) float32 vectors or None each, added to the heads first; ``pairs``: channels
     2j and 2j + 1 turn together instead of j and j + rotary_dim / 2; ``value_dim``: size of a value
     head if it is not ``head_dim``; ``span``: the norm runs over all heads of q together (``q_weight`` of
-    heads * head_dim) and over all heads of k together, not per head.  With any of them the rows may be
-    wider than q, k and v (what follows them is left alone)."""
+    heads * head_dim) and over all heads of k together, not per head; ``v_share`` > 1: that many consecutive
+    key heads read one value head, so the row and the value plane hold kv_heads / v_share value heads.  With any
+    of them the rows may be wider than q, k and v (what follows them is left alone)."""
     _need(qkv, "qkv", dim=2, contiguous=False)
     rows = qkv.shape[0]
     dv = head_dim if value_dim is None else int(value_dim)
-    general = biases is not None or pairs or dv != head_dim or span
-    used = (heads + kv_heads) * head_dim + kv_heads * dv
+    v_share = max(1, int(v_share))
+    if kv_heads % v_share:
+        raise KernelError(f"qk_norm_rope: {kv_heads} key heads share value heads by {v_share}")
+    v_heads = kv_heads // v_share
+    general = biases is not None or pairs or dv != head_dim or span or v_share > 1
+    used = (heads + kv_heads) * head_dim + v_heads * dv
     if qkv.stride(1) != 1 or (qkv.shape[1] < used if general else (qkv.shape[1] != used or not qkv.is_contiguous())):
         raise KernelError(f"qk_norm_rope: qkv {tuple(qkv.shape)} for {heads}+{kv_heads} heads of {head_dim} and {kv_heads} of {dv}")
     q_b, k_b, v_b = biases if biases is not None else (None, None, None)
-    for t, nm, n in ((q_b, "q bias", heads * head_dim), (k_b, "k bias", kv_heads * head_dim), (v_b, "v bias", kv_heads * dv)):
+    for t, nm, n in ((q_b, "q bias", heads * head_dim), (k_b, "k bias", kv_heads * head_dim), (v_b, "v bias", v_heads * dv)):
         if t is not None:
             _need(t, nm, torch.float32, 1)
             if t.numel() != n:
@@ -590,10 +595,10 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
         _need(t, nm, torch.int32, 1)
     _need(block_table, "block table", torch.int32, 2)
     if write_kv:
-        for t, nm, n in ((k_plane, "key plane", head_dim), (v_plane, "value plane", dv)):
+        for t, nm, n, nh in ((k_plane, "key plane", head_dim, kv_heads), (v_plane, "value plane", dv, v_heads)):
             _need(t, nm, qkv.dtype, 4)
-            if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != n:
-                raise KernelError(f"qk_norm_rope: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {n}")
+            if t.shape[1] != nh or t.shape[2] != PAGE or t.shape[3] != n:
+                raise KernelError(f"qk_norm_rope: {nm} {tuple(t.shape)} for {nh} kv heads of {n}")
     p = _QkRopeParams(qkv.data_ptr(), qkv.stride(0), 0 if q_weight is None else q_weight.data_ptr(),
                       0 if k_weight is None else k_weight.data_ptr(), eps,
                       0 if cos is None else cos.data_ptr(), 0 if sin is None else sin.data_ptr(), rotary_dim,
@@ -603,7 +608,7 @@ def _rope_params(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int,
                       1 if write_kv else 0, rows, heads, kv_heads, head_dim,
                       0 if k_plane is None else k_plane.shape[0], block_table.shape[0],
                       0 if q_b is None else q_b.data_ptr(), 0 if k_b is None else k_b.data_ptr(),
-                      0 if v_b is None else v_b.data_ptr(), 1 if pairs else 0, dv, 1 if span else 0)
+                      0 if v_b is None else v_b.data_ptr(), 1 if pairs else 0, dv, 1 if span else 0, v_share)
     return p
 
 
@@ -624,6 +629,7 @@ class _AttnParams(Structure):
         ("seq_kv_len", c_void_p), ("nseq", c_int), ("heads", c_int), ("kv_heads", c_int), ("d", c_int),
         ("max_q_len", c_int), ("scale", c_float), ("window", c_int), ("num_splits", c_int), ("scratch", c_void_p),
         ("pages", c_int), ("max_slots", c_int), ("dv", c_int), ("keep_first", c_int), ("sink", c_int), ("sinks", c_void_p),
+        ("chunk", c_int), ("v_share", c_int), ("v_row_stride", c_int64),
     ]
 
 
@@ -636,10 +642,14 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
                  seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
                  heads: int, kv_heads: int, head_dim: int, scale: float, window: int,
                  num_splits: int, scratch: Optional[torch.Tensor], value_dim: Optional[int] = None, keep_first: int = 0,
-                 sink: bool = False, sinks: Optional[torch.Tensor] = None) -> "_AttnParams":
+                 sink: bool = False, sinks: Optional[torch.Tensor] = None, chunk: int = 0, v_share: int = 1) -> "_AttnParams":
     """``value_dim``: size of a value head if it is not ``head_dim``; ``keep_first``: with a window, keys
     at positions below it stay visible; ``sink``: one more unit in the softmax denominator; ``sinks``
-    (float32 [heads]): head h's denominator holds exp(sinks[h]) instead of that unit."""
+    (float32 [heads]): head h's denominator holds exp(sinks[h]) instead of that unit; ``chunk`` > 0: row i
+    sees key j <= i only if both lie in the same block of ``chunk`` positions counted from the sequence's
+    start; ``v_share`` > 1: that many consecutive key heads read one value head (the value plane holds
+    kv_heads / v_share heads).  The value plane may be a view whose tokens lie further apart than
+    ``value_dim`` (the first channels of a wider plane, the key plane itself for instance)."""
     _need(q, "attention q", dim=2, contiguous=False)
     _need(out, "attention out", q.dtype, 2, contiguous=False)
     dv = head_dim if value_dim is None else int(value_dim)
@@ -651,10 +661,17 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
         _need(sinks, "sink scores", torch.float32, 1)
         if sinks.numel() != heads:
             raise KernelError(f"attention: {sinks.numel()} sink scores for {heads} heads")
-    for t, nm, n in ((k_plane, "key plane", head_dim), (v_plane, "value plane", dv)):
-        _need(t, nm, q.dtype, 4)
-        if t.shape[1] != kv_heads or t.shape[2] != PAGE or t.shape[3] != n:
-            raise KernelError(f"attention: {nm} {tuple(t.shape)} for {kv_heads} kv heads of {n}")
+    v_share = max(1, int(v_share))
+    if chunk < 0 or kv_heads % v_share:
+        raise KernelError(f"attention: blocks of {chunk} positions, {kv_heads} key heads sharing value heads by {v_share}")
+    _need(k_plane, "key plane", q.dtype, 4)
+    _need(v_plane, "value plane", q.dtype, 4, contiguous=False)
+    for t, nm, n, nh in ((k_plane, "key plane", head_dim, kv_heads), (v_plane, "value plane", dv, kv_heads // v_share)):
+        if t.shape[1] != nh or t.shape[2] != PAGE or t.shape[3] != n:
+            raise KernelError(f"attention: {nm} {tuple(t.shape)} for {nh} kv heads of {n}")
+    v_tok = v_plane.stride(2)
+    if v_plane.stride(3) != 1 or v_tok < dv or v_plane.stride(1) != PAGE * v_tok or v_plane.stride(0) != v_plane.shape[1] * PAGE * v_tok:
+        raise KernelError(f"attention: value plane with strides {tuple(v_plane.stride())}")
     for t, nm in ((seq_slot, "seq_slot"), (seq_q_start, "seq_q_start"), (seq_q_len, "seq_q_len"),
                   (seq_kv_len, "seq_kv_len")):
         _need(t, nm, torch.int32, 1)
@@ -672,7 +689,8 @@ def _attn_params(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_pl
                     seq_q_start.data_ptr(), seq_q_len.data_ptr(), seq_kv_len.data_ptr(), nseq, heads, kv_heads,
                     head_dim, max_q_len, scale, window, num_splits, 0 if scratch is None else scratch.data_ptr(),
                     k_plane.shape[0], block_table.shape[0], 0 if dv == head_dim else dv, int(keep_first) if window > 0 else 0,
-                    1 if sink or sinks is not None else 0, 0 if sinks is None else sinks.data_ptr())
+                    1 if sink or sinks is not None else 0, 0 if sinks is None else sinks.data_ptr(),
+                    int(chunk), v_share, 0 if v_tok == dv else v_tok)
     return p
 
 
@@ -681,11 +699,12 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
               seq_q_len: torch.Tensor, seq_kv_len: torch.Tensor, nseq: int, max_q_len: int,
               heads: int, kv_heads: int, head_dim: int, scale: float, window: int = 0,
               num_splits: int = 1, scratch: Optional[torch.Tensor] = None, algo: str = "auto",
-              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False, sinks: Optional[torch.Tensor] = None) -> str:
+              value_dim: Optional[int] = None, keep_first: int = 0, sink: bool = False, sinks: Optional[torch.Tensor] = None,
+              chunk: int = 0, v_share: int = 1) -> str:
     """Causal GQA over the paged cache.  q is a [rows, >= heads*head_dim] view (row stride free),
     out is [rows, heads*value_dim].  Returns the kernel's name."""
     p = _attn_params(q, out, k_plane, v_plane, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, nseq, max_q_len,
-                     heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink, sinks)
+                     heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink, sinks, chunk, v_share)
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
         algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo_x(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
@@ -1238,11 +1257,11 @@ class _MoeRouteParams(Structure):
 class _MoeRowsParams(Structure):
     _fields_ = [("x", c_void_p), ("x_stride", c_int64), ("up", c_void_p), ("down", c_void_p), ("act", c_void_p), ("out", c_void_p),
                 ("out_stride", c_int64), ("index", c_void_p), ("weight", c_void_p), ("rows", c_int), ("experts", c_int), ("top", c_int),
-                ("ff", c_int), ("hidden", c_int), ("act_kind", c_int), ("weight_input", c_int)]
+                ("ff", c_int), ("hidden", c_int), ("act_kind", c_int), ("weight_input", c_int), ("limit", c_float), ("slope", c_float)]
 
 
 MOE_SCORES = {"softmax": 0, "sigmoid": 1}
-MOE_ACTS = {"relu2": 0, "swiglu": 1}
+MOE_ACTS = {"relu2": 0, "swiglu": 1, "glu_clamp": 2}     # the last two are gated: an expert's gate rows, then its up rows
 
 
 def moe_route(logits: torch.Tensor, top: int, renorm_eps: float, dense: torch.Tensor, index: torch.Tensor, weight: torch.Tensor,
@@ -1264,32 +1283,34 @@ def moe_route(logits: torch.Tensor, top: int, renorm_eps: float, dense: torch.Te
 
 
 def moe_act(up: torch.Tensor, dense: Optional[torch.Tensor], act: torch.Tensor, experts: int, ff: int, kind: str = "relu2",
-            weight_input: bool = False) -> None:
+            weight_input: bool = False, limit: float = 0.0, slope: float = 1.0) -> None:
     """act[r, e * ff + i] = dense[r, e] * relu(up[r, e * ff + i])^2 (``act`` may be ``up``).  ``kind`` "swiglu": ``up``
     holds, for each expert, ff gate columns and then ff up columns, and the activation is silu(gate) * up (``act`` is
     then another tensor).  ``weight_input``: the weight multiplies the expert's input (its products) instead of its
-    result.  ``dense`` None: weights of 1."""
+    result.  ``kind`` "glu_clamp": the same layout, g * sigmoid(slope * g) * (v + 1) with g = min(gate, limit) and
+    v = clamp(up, -limit, limit).  ``dense`` None: weights of 1."""
     _need(up, "expert pre-activations", dim=2, contiguous=False)
     _need(act, "expert activations", up.dtype, 2, contiguous=False)
     if dense is not None:
         _need(dense, "expert weights", torch.float32, 2)
     rows = up.shape[0]
-    per = 2 if kind == "swiglu" else 1
+    per = 1 if kind == "relu2" else 2
     if (up.shape != (rows, experts * ff * per) or act.shape != (rows, experts * ff) or (dense is not None and dense.shape != (rows, experts))
             or up.stride(1) != 1 or act.stride(1) != 1 or (per == 2 and act.data_ptr() == up.data_ptr())):
         raise KernelError(f"moe_act: up {tuple(up.shape)}, act {tuple(act.shape)} for {experts} experts of {ff} ({kind})")
-    _check(_lib.gb_moe_act_kind(_ptr(up), c_int64(up.stride(0)), _ptr(dense), _ptr(act), c_int64(act.stride(0)), c_int(rows), c_int(experts),
-                                c_int(ff), c_int(MOE_ACTS[kind]), c_int(1 if weight_input else 0), _code(up.dtype), _stream()))
+    _check(_lib.gb_moe_act_clamped(_ptr(up), c_int64(up.stride(0)), _ptr(dense), _ptr(act), c_int64(act.stride(0)), c_int(rows), c_int(experts),
+                                   c_int(ff), c_int(MOE_ACTS[kind]), c_int(1 if weight_input else 0), c_float(limit), c_float(slope),
+                                   _code(up.dtype), _stream()))
 
 
 def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
-             experts: int, ff: int, kind: str = "relu2", weight_input: bool = False) -> None:
+             experts: int, ff: int, kind: str = "relu2", weight_input: bool = False, limit: float = 0.0, slope: float = 1.0) -> None:
     """The experts' feed-forward for a step of few rows, reading only the chosen experts' matrices:
     out[r] = sum_k weight[r, k] * down_e(relu(up_e x[r])^2), e = index[r, k].  ``up`` is [experts * ff, hidden]
     (the up matrices one above the other), ``down`` [hidden, experts * ff] (the down matrices side by side),
     ``out`` float32 [rows, hidden].  ``kind`` "swiglu": gated experts, ``up`` [experts * 2 ff, hidden] with each
     expert's gate rows ahead of its up rows; ``weight_input``: the weight multiplies the expert's input."""
-    per = 2 if kind == "swiglu" else 1
+    per = 1 if kind == "relu2" else 2
     _need(x, "moe x", dim=2, contiguous=False)
     _need(up, "stacked up matrices", dim=2)
     _need(down, "stacked down matrices", up.dtype, 2)
@@ -1303,18 +1324,19 @@ def moe_rows(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, index: torch
         raise KernelError(f"moe_rows: x {tuple(x.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, out {tuple(out.shape)}")
     act = torch.empty((rows, top, ff), dtype=x.dtype, device=x.device)
     p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), out.data_ptr(), out.stride(0),
-                       index.data_ptr(), weight.data_ptr(), rows, experts, top, ff, hidden, MOE_ACTS[kind], 1 if weight_input else 0)
+                       index.data_ptr(), weight.data_ptr(), rows, experts, top, ff, hidden, MOE_ACTS[kind], 1 if weight_input else 0, limit, slope)
     _check(_lib.gb_moe_rows(byref(p), _code(x.dtype), _code(up.dtype), _stream()), 2)
 
 
 def moe_rows_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, offsets: torch.Tensor, src_row: torch.Tensor, ys: torch.Tensor,
-                     experts: int, top: int, ff: int, kind: str = "relu2", sorted_weight: Optional[torch.Tensor] = None) -> None:
+                     experts: int, top: int, ff: int, kind: str = "relu2", sorted_weight: Optional[torch.Tensor] = None,
+                     limit: float = 0.0, slope: float = 1.0) -> None:
     """The few-row feed-forward with the (row, choice) pairs sorted by expert (``offsets`` and ``src_row`` from
     ``moe_group``): every expert's matrices are read once, ``ys`` (float32 [rows * top, hidden]) receives each pair's
     output down_e(relu(up_e x)^2) at its sorted place; ``moe_combine`` adds a row's pairs up with their weights.
     ``kind`` as for ``moe_rows``; ``sorted_weight`` (float32 [rows * top], the pairs' weights in sorted order): the
     weight multiplies the expert's input here, and ``moe_combine`` then adds up without weights."""
-    per = 2 if kind == "swiglu" else 1
+    per = 1 if kind == "relu2" else 2
     if sorted_weight is not None:
         _need(sorted_weight, "sorted weights", torch.float32, 1)
     _need(x, "moe x", dim=2, contiguous=False)
@@ -1330,7 +1352,7 @@ def moe_rows_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, offs
     act = torch.empty((rows * top, ff), dtype=x.dtype, device=x.device)
     p = _MoeRowsParams(x.data_ptr(), x.stride(0), up.data_ptr(), down.data_ptr(), act.data_ptr(), 0, 0, 0,
                        0 if sorted_weight is None else sorted_weight.data_ptr(), rows, experts, top, ff, hidden, MOE_ACTS[kind],
-                       0 if sorted_weight is None else 1)
+                       0 if sorted_weight is None else 1, limit, slope)
     _check(_lib.gb_moe_rows_grouped(byref(p), _ptr(offsets), _ptr(src_row), _ptr(ys), _code(x.dtype), _code(up.dtype), _stream()), 2)
 
 
@@ -1455,3 +1477,120 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: t
     _check(_lib.gb_gemm_tc5_grouped(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), _ptr(offsets), c_int(groups), c_int(P), c_int(N), c_int(K),
                                     c_int64(a.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(block), c_int(1 if by_cols else 0),
                                     c_int(1 if gated else 0), _ptr(row_weight), _ptr(row_map), _stream()))
+
+
+# ---- layers with the norm behind the sublayer, differential and latent attention ----------------
+def norm_scale_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, x_out: Optional[torch.Tensor] = None) -> None:
+    """h += y / sqrt(mean(y^2) + eps) * weight on float32 rows (``weight``: the norm's weight with the sublayer's
+    constant factors folded in); with ``x_out`` the new rows are left there too, in its dtype, for whoever reads
+    the residual next."""
+    _need(h, "residual", torch.float32, 2)
+    _need(y, "sublayer output", torch.float32, 2)
+    _need(weight, "norm weight", torch.float32, 1)
+    rows, n = h.shape
+    if y.shape != h.shape or weight.numel() != n:
+        raise KernelError(f"norm_scale_add: h {tuple(h.shape)}, y {tuple(y.shape)}, weight {tuple(weight.shape)}")
+    if x_out is not None:
+        _need(x_out, "rows out", dim=2)
+        if x_out.shape != h.shape:
+            raise KernelError(f"norm_scale_add: rows out {tuple(x_out.shape)} for h {tuple(h.shape)}")
+    _check(_lib.gb_norm_scale_add(_ptr(h), _ptr(y), _ptr(weight), c_float(eps), c_int(rows), c_int(n), _ptr(x_out),
+                                  c_int(F32 if x_out is None else _code(x_out.dtype)), _stream()))
+
+
+def diff_combine(ctx: torch.Tensor, out: torch.Tensor, heads: int, per_group: int, value_dim: int, lam: float, eps: float, factor: float) -> None:
+    """The two softmax maps of every head combined: o = a1 - lam * a2, o / sqrt(mean(o^2) + eps) * factor.  ``ctx`` is
+    the attention output [rows, 2 * heads * value_dim] with the heads of a key group ordered [map 1 of each of its
+    ``per_group`` heads, map 2 of each]; ``out`` [rows, heads * value_dim] in the model's head order."""
+    _need(ctx, "attention maps", dim=2, contiguous=False)
+    _need(out, "combined heads", ctx.dtype, 2, contiguous=False)
+    rows = ctx.shape[0]
+    if (ctx.shape[1] != 2 * heads * value_dim or out.shape != (rows, heads * value_dim) or ctx.stride(1) != 1 or out.stride(1) != 1
+            or per_group <= 0 or heads % per_group):
+        raise KernelError(f"diff_combine: maps {tuple(ctx.shape)}, out {tuple(out.shape)} for {heads} heads of {value_dim} in groups of {per_group}")
+    _check(_lib.gb_diff_combine(_ptr(ctx), c_int64(ctx.stride(0)), _ptr(out), c_int64(out.stride(0)), c_int(rows), c_int(heads), c_int(per_group),
+                                c_int(value_dim), c_float(lam), c_float(eps), c_float(factor), _code(ctx.dtype), _stream()))
+
+
+def add_rows_gated(out: torch.Tensor, y: torch.Tensor, z: torch.Tensor) -> None:
+    """out[r] += sigmoid(z[r]) * y[r]; ``z`` float32 [rows] (a view with a free stride)."""
+    _need(out, "sum", torch.float32, 2)
+    _need(y, "addend", torch.float32, 2)
+    _need(z, "gate", torch.float32, 1, contiguous=False)
+    if y.shape != out.shape or z.numel() != out.shape[0]:
+        raise KernelError(f"add_rows_gated: out {tuple(out.shape)}, y {tuple(y.shape)}, gate {tuple(z.shape)}")
+    _check(_lib.gb_add_rows_gated(_ptr(out), _ptr(y), _ptr(z), c_int64(z.stride(0)), c_int(out.shape[0]), c_int(out.shape[1]), _stream()))
+
+
+def latent_prep(lat: torch.Tensor, cq: torch.Tensor, q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float, cos: Optional[torch.Tensor],
+                sin: Optional[torch.Tensor], q_rank: int, kv_rank: int, rot: int, row_pos: torch.Tensor, row_seq: torch.Tensor,
+                seq_slot: torch.Tensor, block_table: torch.Tensor, k_plane: Optional[torch.Tensor], write_kv: bool) -> None:
+    """Rows of a fused down-projection [q latent | kv latent | rotated key part]: the q latent RMS-normed with
+    ``q_weight`` into ``cq``; the kv latent RMS-normed with ``kv_weight`` and the key part rotated (channels 2j and
+    2j + 1 by angle j of the tables) into ``k_plane`` ([pages, 1, 64, kv_rank + rot]) at each row's position."""
+    _need(lat, "latents", dim=2, contiguous=False)
+    _need(cq, "q latent", lat.dtype, 2)
+    _need(q_weight, "q latent norm", torch.float32, 1)
+    _need(kv_weight, "kv latent norm", torch.float32, 1)
+    rows = lat.shape[0]
+    if (lat.shape[1] < q_rank + kv_rank + rot or lat.stride(1) != 1 or cq.shape != (rows, q_rank) or q_weight.numel() != q_rank
+            or kv_weight.numel() != kv_rank):
+        raise KernelError(f"latent_prep: latents {tuple(lat.shape)}, q latent {tuple(cq.shape)} for ranks {q_rank}, {kv_rank} and {rot} rotated channels")
+    tp = 0
+    if rot > 0:
+        _need(cos, "rope cos", torch.float32, 2)
+        _need(sin, "rope sin", torch.float32, 2)
+        if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+            raise KernelError(f"latent_prep: angle tables {tuple(cos.shape)} for {rot} rotated channels")
+        tp = cos.shape[0]
+    for t, nm in ((row_pos, "row_pos"), (row_seq, "row_seq"), (seq_slot, "seq_slot")):
+        _need(t, nm, torch.int32, 1)
+    _need(block_table, "block table", torch.int32, 2)
+    if write_kv:
+        _need(k_plane, "key plane", lat.dtype, 4)
+        if tuple(k_plane.shape[1:]) != (1, PAGE, kv_rank + rot):
+            raise KernelError(f"latent_prep: key plane {tuple(k_plane.shape)} for a latent of {kv_rank} + {rot}")
+    _check(_lib.gb_latent_prep(_ptr(lat), c_int64(lat.stride(0)), _ptr(cq), _ptr(q_weight), _ptr(kv_weight), c_float(eps), _ptr(cos), _ptr(sin),
+                               c_int(tp), _ptr(row_pos), _ptr(row_seq), _ptr(seq_slot), _ptr(block_table), c_int(block_table.stride(0)),
+                               _ptr(k_plane if write_kv else None), c_int(1 if write_kv else 0), c_int(rows), c_int(q_rank), c_int(kv_rank),
+                               c_int(rot), c_int(k_plane.shape[0] if write_kv else 0), c_int(block_table.shape[0]), _code(lat.dtype), _stream()))
+
+
+def latent_q_rot(q: torch.Tensor, out: torch.Tensor, heads: int, head_dim: int, rot: int, cos: torch.Tensor, sin: torch.Tensor,
+                 row_pos: torch.Tensor) -> None:
+    """The last ``rot`` channels of every query head of ``q`` ([rows, heads * (head_dim + rot)]) rotated by the row's
+    position (channels 2j and 2j + 1 together) into the last ``rot`` channels of every head of ``out``
+    ([rows, heads * out_head])."""
+    _need(q, "queries", dim=2, contiguous=False)
+    _need(out, "absorbed queries", q.dtype, 2, contiguous=False)
+    rows = q.shape[0]
+    if rot <= 0:
+        return
+    out_head = out.shape[1] // heads
+    if q.shape[1] != heads * (head_dim + rot) or out.shape[1] != heads * out_head or out_head < rot or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"latent_q_rot: q {tuple(q.shape)}, out {tuple(out.shape)} for {heads} heads of {head_dim} + {rot}")
+    _need(cos, "rope cos", torch.float32, 2)
+    _need(sin, "rope sin", torch.float32, 2)
+    _need(row_pos, "row_pos", torch.int32, 1)
+    if cos.shape[1] != rot // 2 or sin.shape != cos.shape:
+        raise KernelError(f"latent_q_rot: angle tables {tuple(cos.shape)} for {rot} rotated channels")
+    _check(_lib.gb_latent_q_rot(_ptr(q), c_int64(q.stride(0)), _ptr(out), c_int64(out.stride(0)), c_int(rows), c_int(heads), c_int(head_dim),
+                                c_int(rot), c_int(out_head), _ptr(cos), _ptr(sin), c_int(cos.shape[0]), _ptr(row_pos), _code(q.dtype), _stream()))
+
+
+HEAD_GEMM_MAX_K = 1536     # float32 rows of this many channels are what one CTA of the kernel stages
+
+
+def head_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, h, :] = a[r, h, :] @ w[h] for every head in one launch: ``a`` [rows, heads, K] and ``out``
+    [rows, heads, N] may be views with free row and head strides, ``w`` is [heads, K, N]; float32 sums on the
+    CUDA cores."""
+    _need(a, "head_gemm a", dim=3, contiguous=False)
+    _need(w, "head_gemm w", dim=3)
+    _need(out, "head_gemm out", a.dtype, 3, contiguous=False)
+    rows, heads, K = a.shape
+    N = w.shape[2]
+    if w.shape != (heads, K, N) or out.shape != (rows, heads, N) or a.stride(2) != 1 or out.stride(2) != 1 or K > HEAD_GEMM_MAX_K:
+        raise KernelError(f"head_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_head_gemm(_ptr(a), c_int64(a.stride(0)), c_int64(a.stride(1)), _ptr(w), _ptr(out), c_int64(out.stride(0)), c_int64(out.stride(1)),
+                             c_int(rows), c_int(heads), c_int(K), c_int(N), _code(a.dtype), _code(w.dtype), _stream()))

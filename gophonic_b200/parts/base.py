@@ -47,6 +47,9 @@ class KVRequest:
     head_dim: int
     window: int = 0
     value_dim: int = 0
+    value_heads: int = 0          # value heads a token has if not ``kv_heads`` (several key heads may read one value head)
+    values_in_keys: bool = False  # the values are the first ``value_dim`` channels of the keys: no value plane is kept,
+                                  # the run's ``v`` is a view of its key plane
 
 
 @dataclass(frozen=True)
@@ -109,6 +112,14 @@ def fold_weight(norm, width: int) -> Optional[torch.Tensor]:
     if fold is None or fold[0].numel() != width:
         return None
     return fold[0]
+
+
+@dataclass
+class ActRows:
+    """What a block may hand on instead of an addend: nothing is owed to the residual, and ``x`` holds its rows
+    once more in the activation dtype (the kernel that changed the residual last wrote them in the same pass), so
+    a block whose sublayers read the residual itself need not convert them again.  Blocks that norm first ignore it."""
+    x: torch.Tensor
 
 
 @dataclass

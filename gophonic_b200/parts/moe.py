@@ -2,7 +2,9 @@
 highest, out = sum over the chosen e of weight_e * down_e(relu(up_e x)^2).  The spec may ask for sigmoid scores,
 weights that are not renormalised, weights that multiply an expert's input (out = sum expert_e(weight_e x)), gated
 experts down_e(silu(gate_e x) * (up_e x)), whose gate and up matrices are then stacked expert by expert as
-[gate_e; up_e], and a shared expert that every token uses (a ``SwiGLU`` part of its own, added to the sum).
+[gate_e; up_e] (or, ``act`` "glu_clamp", the clamped gate g sigmoid(slope g) (u + 1)), a bias on the router's logits,
+and a shared expert that every token uses (a feed-forward part of its own, whatever kind its spec names, added to the
+sum as it is or times sigmoid(w . x), one number a token; w then rides as one more row of the router's matrix).
 An expert has no biases, so a weight on its input is a factor on the outputs of its first products: it is applied
 to them in float32, inside the activation between the two products.
 
@@ -25,8 +27,9 @@ from typing import List, Mapping
 
 import torch
 
+from .. import registry
 from .base import FeedForward, Runtime, TensorDecl
-from .swiglu import SwiGLU
+from .swiglu import SwiGLU  # noqa: F401  (the shared expert's usual kind)
 
 
 class MoE(FeedForward):
@@ -37,14 +40,18 @@ class MoE(FeedForward):
     @classmethod
     def declare(cls, spec, prefix: str) -> List[TensorDecl]:
         decls = [TensorDecl(prefix + "router", (spec.experts, spec.hidden))]
+        if getattr(spec, "router_bias", False):
+            decls.append(TensorDecl(prefix + "router" + spec.router_bias_suffix, (spec.experts,), role="vector"))
         for e in range(spec.experts):
-            if getattr(spec, "act", "relu2") == "swiglu":
+            if getattr(spec, "act", "relu2") != "relu2":
                 decls.append(TensorDecl(prefix + f"e{e}.gate", (spec.intermediate, spec.hidden)))
             decls += [TensorDecl(prefix + f"e{e}.up", (spec.intermediate, spec.hidden)),
                       TensorDecl(prefix + f"e{e}.down", (spec.hidden, spec.intermediate))]
         shared = getattr(spec, "shared", None)
         if shared is not None:
-            decls += SwiGLU.declare(shared, prefix + spec.shared_prefix)
+            decls += registry.part_class("feed_forward", shared.kind).declare(shared, prefix + spec.shared_prefix)
+            if getattr(spec, "shared_gate", False):
+                decls.append(TensorDecl(prefix + spec.shared_prefix + spec.shared_gate_name, (1, spec.hidden)))
         return decls
 
     def __init__(self, spec, prefix: str, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
@@ -54,10 +61,11 @@ class MoE(FeedForward):
         self.score = getattr(spec, "score", "softmax")
         self.renorm = bool(getattr(spec, "renorm", True))
         self.weight_input = getattr(spec, "weight_on", "output") == "input"
-        if self.act not in ("relu2", "swiglu") or self.score not in ("softmax", "sigmoid") or getattr(spec, "weight_on", "output") not in ("output", "input"):
+        self.limit, self.slope = float(getattr(spec, "act_limit", 0.0)), float(getattr(spec, "act_slope", 1.0))
+        if self.act not in ("relu2", "swiglu", "glu_clamp") or self.score not in ("softmax", "sigmoid") or getattr(spec, "weight_on", "output") not in ("output", "input"):
             raise ValueError(f"{prefix}: unknown activation, score or weight placement in {spec}")
         ups = [tensors[prefix + f"e{e}.up"] for e in range(spec.experts)]
-        if self.act == "swiglu":     # a gated expert's rows: its gate matrix, then its up matrix
+        if self.act != "relu2":      # a gated expert's rows: its gate matrix, then its up matrix
             ups = [t for e in range(spec.experts) for t in (tensors[prefix + f"e{e}.gate"], ups[e])]
         downs = [tensors[prefix + f"e{e}.down"] for e in range(spec.experts)]
         if len({t.dtype for t in ups + downs}) != 1:
@@ -65,8 +73,18 @@ class MoE(FeedForward):
         self.up = torch.cat(ups, dim=0).contiguous()         # [experts * ff, hidden]
         self.down = torch.cat(downs, dim=1).contiguous()     # [hidden, experts * ff]
         self.router = tensors[prefix + "router"].contiguous()
+        self.router_bias = None
+        if getattr(spec, "router_bias", False):
+            self.router_bias = tensors[prefix + "router" + spec.router_bias_suffix].to(torch.float32).contiguous()
         shared = getattr(spec, "shared", None)
-        self.shared = None if shared is None else SwiGLU(shared, prefix + spec.shared_prefix, tensors, runtime)
+        self.shared = None if shared is None else registry.part_class("feed_forward", shared.kind)(shared, prefix + spec.shared_prefix, tensors, runtime)
+        self.shared_gated = shared is not None and bool(getattr(spec, "shared_gate", False))
+        if self.shared_gated:
+            # the gate's vector is one more row of the router's matrix: one product gives the logits and the gate's pre-activation
+            gate = tensors[prefix + spec.shared_prefix + spec.shared_gate_name].reshape(1, spec.hidden).to(self.router.dtype)
+            self.router = torch.cat([self.router, gate], dim=0).contiguous()
+            if self.router_bias is not None:
+                self.router_bias = torch.cat([self.router_bias, torch.zeros(1, dtype=torch.float32, device=self.router_bias.device)]).contiguous()
 
     def weight_bytes(self) -> int:
         """Bytes of the matrices a token's step reads: the router and the chosen experts."""
@@ -75,7 +93,12 @@ class MoE(FeedForward):
         return self.router.numel() * self.router.element_size() + per * self.spec.top + shared
 
     def forward(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
-        self._experts(batch, x, out)
+        logits = self._experts(batch, x, out)
+        if self.shared_gated:
+            both = torch.empty_like(out)
+            self.shared.forward(batch, x, both)
+            self.rt.ops.add_rows_gated(out, both, logits[:, self.spec.experts])
+            return
         if self.shared is not None:
             if out.dtype == torch.float32 and self.shared.adds_in_place(x.shape[0]):
                 self.shared.forward_into(batch, x, out)     # its last product adds into the experts' sum
@@ -84,19 +107,23 @@ class MoE(FeedForward):
             self.shared.forward(batch, x, both)
             self.rt.ops.add_rows(out, both)
 
-    def _experts(self, batch, x: torch.Tensor, out: torch.Tensor) -> None:
+    def _experts(self, batch, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        """The chosen experts' weighted sum into ``out``; returns what the router's product left (the experts' logits and,
+        behind them, the shared expert's gate pre-activation if there is one)."""
         ops, s = self.rt.ops, self.spec
         rows = x.shape[0]
-        logits = torch.empty((rows, s.experts), dtype=torch.float32, device=x.device)
-        ops.gemm(x, self.router, logits)
+        every = torch.empty((rows, self.router.shape[0]), dtype=torch.float32, device=x.device)
+        ops.gemm(x, self.router, every, bias=self.router_bias)
+        logits = every[:, :s.experts]
+        kw = dict(kind=self.act, limit=self.limit, slope=self.slope)
         dense = torch.empty((rows, s.experts), dtype=torch.float32, device=x.device)
         index = torch.empty((rows, s.top), dtype=torch.int32, device=x.device)
         weight = torch.empty((rows, s.top), dtype=torch.float32, device=x.device)
         ops.moe_route(logits, s.top, float(s.renorm_eps), dense, index, weight, score=self.score, renorm=self.renorm)
         if rows <= self.ROWS_SPARSE and s.top < s.experts:
             if rows * s.top <= s.experts:      # hardly two pairs with one expert: a pair reads its expert's matrices
-                ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate, kind=self.act, weight_input=self.weight_input)
-                return
+                ops.moe_rows(x, self.up, self.down, index, weight, out, s.experts, s.intermediate, weight_input=self.weight_input, **kw)
+                return every
             # more pairs than experts: sorted by expert on the device, every expert's matrices are read once
             pairs = rows * s.top
             offsets = torch.empty(s.experts + 1, dtype=torch.int32, device=x.device)
@@ -105,18 +132,18 @@ class MoE(FeedForward):
             sorted_w = torch.empty(pairs, dtype=torch.float32, device=x.device) if self.weight_input else None
             ops.moe_group(index, s.experts, offsets, place, src_row, weight if self.weight_input else None, sorted_w)
             ys = torch.empty((pairs, s.hidden), dtype=torch.float32, device=x.device)
-            ops.moe_rows_grouped(x, self.up, self.down, offsets, src_row, ys, s.experts, s.top, s.intermediate, kind=self.act,
-                                 sorted_weight=sorted_w)
+            ops.moe_rows_grouped(x, self.up, self.down, offsets, src_row, ys, s.experts, s.top, s.intermediate, sorted_weight=sorted_w, **kw)
             ops.moe_combine(ys, place, None if self.weight_input else weight, out, top=s.top)
-            return
+            return every
         if rows >= self.ROWS_GROUPED and s.top < s.experts and (self._one_launch(x.dtype) or not torch.cuda.is_current_stream_capturing()):
             self._grouped(x, index, weight, out)
-            return
+            return every
         up = torch.empty((rows, self.up.shape[0]), dtype=x.dtype, device=x.device)
         ops.gemm(x, self.up, up)
         act = up if self.act == "relu2" else torch.empty((rows, s.experts * s.intermediate), dtype=x.dtype, device=x.device)
-        ops.moe_act(up, dense, act, s.experts, s.intermediate, kind=self.act, weight_input=self.weight_input)
+        ops.moe_act(up, dense, act, s.experts, s.intermediate, weight_input=self.weight_input, **kw)
         ops.gemm(act, self.down, out)
+        return every
 
     def _grouped(self, x: torch.Tensor, index: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         """Every expert on its own rows: sort the pairs by expert, gather, two products over the groups, add up."""
@@ -151,7 +178,8 @@ class MoE(FeedForward):
             else:
                 # every sorted pair is a row of one "expert" here: its own weight (or 1), its own activation
                 made = act if self.act == "relu2" else torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
-                ops.moe_act(act, None if sorted_w is None else sorted_w.view(pairs, 1), made, 1, ff, kind=self.act, weight_input=self.weight_input)
+                ops.moe_act(act, None if sorted_w is None else sorted_w.view(pairs, 1), made, 1, ff, kind=self.act, weight_input=self.weight_input,
+                            limit=self.limit, slope=self.slope)
                 act = made
         if one_launch:
             if s.top == 1 and self.weight_input:

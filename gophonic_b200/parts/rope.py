@@ -6,6 +6,8 @@ cosines and sines rounded to fp32 tables (internal/qwen3lm/weights.go:681-688;
 internal/qwen3lm/evaluator.go:847-858).  The tables are consumed by the fused
 norm + rotation + cache-write kernel; this part only owns them.
 
+With ``scaling`` in the spec the slow frequencies are stretched for long contexts (``scaled_frequencies``).
+
 ``NoPosition``: nothing is applied.
 """
 from __future__ import annotations
@@ -16,6 +18,20 @@ import numpy as np
 import torch
 
 from .base import PositionEncoding, Runtime
+
+
+def scaled_frequencies(freq: np.ndarray, scaling) -> np.ndarray:
+    """Frequencies stretched for long contexts: ``scaling`` = (factor, low, high, original).  A frequency whose
+    wavelength is longer than original / low is divided by factor, one whose wavelength is shorter than
+    original / high stays, and between the two s = (original / wavelength - low) / (high - low) blends the divided
+    and the plain frequency, (1 - s) f / factor + s f.  float64; None: as they are."""
+    if scaling is None:
+        return freq
+    factor, low, high, original = (float(v) for v in scaling)
+    wave = 2.0 * np.pi / freq
+    s = (original / wave - low) / (high - low)
+    out = np.where(wave < original / high, freq, np.where(wave > original / low, freq / factor, (1.0 - s) * freq / factor + s * freq))
+    return out
 
 
 class RotaryEmbedding(PositionEncoding):
@@ -33,7 +49,7 @@ class RotaryEmbedding(PositionEncoding):
             return
         rot = self.spec.rotary_dim
         i = np.arange(rot // 2, dtype=np.float64)
-        inv_freq = 1.0 / np.power(float(self.spec.theta), 2.0 * i / float(rot))
+        inv_freq = scaled_frequencies(1.0 / np.power(float(self.spec.theta), 2.0 * i / float(rot)), getattr(self.spec, "scaling", None))
         ang = np.arange(capacity, dtype=np.float64)[:, None] * inv_freq[None, :]
         self.cos = torch.from_numpy(np.cos(ang).astype(np.float32)).to(self.rt.device)
         self.sin = torch.from_numpy(np.sin(ang).astype(np.float32)).to(self.rt.device)

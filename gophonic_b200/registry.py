@@ -125,10 +125,12 @@ def _register_builtin() -> None:
     from .config.pugalix import PugalixConfig
     from .config.vepitar import VepitarConfig
     from .config.kalonex import KalonexConfig
+    from .config.kimilix import KimilixConfig
     register_architecture("Qwen3ForCausalLM", Qwen3Config, model_type="qwen3")
     register_architecture("Pugalix", PugalixConfig)
     register_architecture("Vepitar", VepitarConfig)
     register_architecture("Kalonex", KalonexConfig)
+    register_architecture("Kimilix", KimilixConfig)
 
 
 _register_builtin()
