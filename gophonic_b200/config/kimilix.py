@@ -90,6 +90,7 @@ class KimilixConfig:
     residual_mult: float
     layers: Tuple[KimilixLayer, ...]
     architecture: str = "Kimilix"
+    tie_word_embeddings = True              # the head is the embedding table (no field: the file has no such key)
 
     # ---- reading -------------------------------------------------------------------------
     @classmethod

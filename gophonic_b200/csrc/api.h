@@ -183,6 +183,8 @@ GB_API int gb_attention_decode_mma_x(const AttnParamsX* p, cudaStream_t stream);
 GB_API int gb_attention_prefill_mma_x(const AttnParamsX* p, cudaStream_t stream);
 GB_API int gb_attention_prefill_tc5_x(const AttnParamsX* p, int rows, int pages, cudaStream_t stream);
 GB_API int gb_attention_algo_x(const AttnParamsX* p, int dtype);
+GB_API int gb_attention_latent_accepts(const AttnParamsX* p, int dtype);
+GB_API int gb_attention_latent_mma(const AttnParamsX* p, cudaStream_t stream);
 
 // an AttnParams as the kernels take it: the later options off
 static inline AttnParamsX gb_attn_widen(const AttnParams& a) {

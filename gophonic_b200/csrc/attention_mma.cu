@@ -77,6 +77,11 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParamsX p) {
         lo_pos = past + q0 - p.window + 1;
         if (lo_pos < 0) lo_pos = 0;
     }
+    if (p.chunk > 0) {
+        // blocks of positions: the block of the tile's first row begins no later than any other row's
+        const int b = (past + q0) - (past + q0) % p.chunk;
+        if (b > lo_pos) lo_pos = b;
+    }
     const int t_lo = lo_pos / 64, t_hi = hi_pos / 64;
     // with kept first tokens: the tiles of keys [0, keep_first) first, then those of the window, each once
     int n_first = p.window > 0 && p.keep_first > 0 ? (p.keep_first + 63) / 64 : 0;
@@ -87,8 +92,10 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParamsX p) {
     auto load_tile = [&](int t, int buf) {
         int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
+        // consecutive key heads may read one value head
+        int64_t voff = p.v_share > 1 ? ((page * (p.kv_heads / p.v_share) + kvh / p.v_share) * 64) * (int64_t)HD : off;
         load_page<HD>(Ks + buf * 64 * SD, kbase + off, tid, 128);
-        load_page<HD>(Vs + buf * 64 * SD, vbase + off, tid, 128);
+        load_page<HD>(Vs + buf * 64 * SD, vbase + voff, tid, 128);
     };
     load_tile(tile_of(0), 0);
     cp_async_commit();
@@ -148,7 +155,7 @@ __global__ void __launch_bounds__(128) attn_prefill_mma_kernel(AttnParamsX p) {
             for (int e = 0; e < 4; e++) {
                 int key = t * 64 + j * 8 + t4 * 2 + (e & 1);
                 int row = (e & 2) ? row1 : row0;
-                bool ok = key <= row && (p.window <= 0 || key > row - p.window || key < p.keep_first);
+                bool ok = key <= row && (p.window <= 0 || key > row - p.window || key < p.keep_first) && (p.chunk <= 0 || key >= row - row % p.chunk);
                 float v = ok ? s[j][e] * sc : -INFINITY;
                 s[j][e] = v;
                 if (e & 2) mx1 = fmaxf(mx1, v); else mx0 = fmaxf(mx0, v);
@@ -340,6 +347,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParamsX p, Rop
         lo_pos = pos - p.window + 1;
         if (lo_pos < 0) lo_pos = 0;
     }
+    if (p.chunk > 0 && pos - pos % p.chunk > lo_pos) lo_pos = pos - pos % p.chunk;   // blocks of positions
     const int t_lo = lo_pos / 64, t_hi = pos / 64 + 1;  // [t_lo, t_hi)
     // with kept first tokens: the tiles of keys [0, keep_first) first, then those of the window; the
     // splits cut this list of tiles
@@ -356,9 +364,10 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(AttnParamsX p, Rop
         int t = tile_of(my_lo + i);
         int64_t page = page_of(bt, t * 64, p.bt_stride, p.pages);
         int64_t off = ((page * p.kv_heads + kvh) * 64) * (int64_t)HD;
+        int64_t voff = p.v_share > 1 ? ((page * (p.kv_heads / p.v_share) + kvh / p.v_share) * 64) * (int64_t)HD : off;
         bf16* st = KV + (i % DSTAGES) * STAGE;
         load_page<HD>(st, kbase + off, tid, 128);
-        load_page<HD>(st + 64 * SD, vbase + off, tid, 128);
+        load_page<HD>(st + 64 * SD, vbase + voff, tid, 128);
     };
     // Without `f.on` the keys of this step were written by the kernel just ahead: nothing is fetched early.
     if (!f.on) pdl_wait();
@@ -639,6 +648,8 @@ int check(const AttnParamsX& p, const char* who) {
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
     if (p.dv && p.dv != p.d) GB_REFUSE("%s: values of another size than keys run on the CUDA-core kernel", who);
     if (p.keep_first < 0) GB_REFUSE("%s: %d kept first tokens", who, p.keep_first);
+    if (p.chunk < 0 || p.v_share < 0 || (p.v_share > 1 && p.kv_heads % p.v_share) || p.v_row_stride > 0)
+        GB_REFUSE("%s: blocks of %d positions, value heads shared by %d, value stride %lld", who, p.chunk, p.v_share, (long long)p.v_row_stride);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if ((p.out_row_stride & 1) || ((uintptr_t)p.out & 3)) GB_REFUSE("%s: output rows must be 4-byte aligned", who);
     return 0;

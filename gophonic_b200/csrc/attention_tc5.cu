@@ -200,6 +200,11 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
         lo_pos = past + q0 - p.window + 1;
         if (lo_pos < 0) lo_pos = 0;
     }
+    if (p.chunk > 0) {
+        // blocks of positions: the block of the CTA's first row begins no later than any other row's
+        const int b = (past + q0) - (past + q0) % p.chunk;
+        if (b > lo_pos) lo_pos = b;
+    }
     const int t_lo = lo_pos / BKV;
     // with kept first tokens: the pages of keys [0, keep_first) first, then those of the window, each once
     int n_first = p.window > 0 && p.keep_first > 0 ? (p.keep_first + BKV - 1) / BKV : 0;
@@ -297,7 +302,9 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
                 unsigned char* vs = KVs + (size_t)s * STAGE_BYTES + K_BYTES;
                 int lp = tile_of(j);
                 if (!gb_check(lp, p.bt_stride, GB_CHECK_LOGICAL_PAGE) || lp >= p.bt_stride) lp = p.bt_stride - 1;
-                const int row = ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * p.kv_heads + kvh) * 64;
+                // consecutive key heads may read one value head
+                const int row = p.v_share > 1 ? ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * (p.kv_heads / p.v_share) + kvh / p.v_share) * 64
+                                              : ((int)page_of(bt, lp * BKV, p.bt_stride, p.pages) * p.kv_heads + kvh) * 64;
 #pragma unroll
                 for (int h = 0; h < 2; h++) tma_load_2d(vs + h * KPANEL, &map_v, h * 64, row, &v_full[s]);
                 issued = j + 1;
@@ -421,13 +428,14 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_tc5_kernel(const __grid_
             tmem_ld32_nowait(s_addr + 32u, v1);
             tmem_wait_ld();
 
-            const bool need_mask = key0 + BKV - 1 > pos || (p.window > 0 && key0 <= pos - p.window);
+            const int block0 = p.chunk > 0 ? pos - pos % p.chunk : 0;     // first position of the row's block
+            const bool need_mask = key0 + BKV - 1 > pos || (p.window > 0 && key0 <= pos - p.window) || key0 < block0;
             if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < 32; i++) {
                     const int ka = key0 + i, kb = key0 + 32 + i;
-                    if (ka > pos || (p.window > 0 && ka <= pos - p.window && ka >= p.keep_first)) v0[i] = 0xff800000u;  // -inf
-                    if (kb > pos || (p.window > 0 && kb <= pos - p.window && kb >= p.keep_first)) v1[i] = 0xff800000u;
+                    if (ka > pos || (p.window > 0 && ka <= pos - p.window && ka >= p.keep_first) || ka < block0) v0[i] = 0xff800000u;  // -inf
+                    if (kb > pos || (p.window > 0 && kb <= pos - p.window && kb >= p.keep_first) || kb < block0) v1[i] = 0xff800000u;
                 }
             }
             bool grow = false;
@@ -607,6 +615,8 @@ static int launch_tc5(const SigmoidAttnParams& p, int rows, int pages, int sigmo
     if (p.window < 0) GB_REFUSE("%s: window %d", who, p.window);
     if (p.dv && p.dv != p.d) GB_REFUSE("%s: values of another size than keys run on the CUDA-core kernel", who);
     if (p.keep_first < 0) GB_REFUSE("%s: %d kept first tokens", who, p.keep_first);
+    if (p.chunk < 0 || p.v_share < 0 || (p.v_share > 1 && p.kv_heads % p.v_share) || p.v_row_stride > 0)
+        GB_REFUSE("%s: blocks of %d positions, value heads shared by %d, value stride %lld", who, p.chunk, p.v_share, (long long)p.v_row_stride);
     if (((uintptr_t)p.q & 15) || (p.q_row_stride & 7)) GB_REFUSE("%s: query rows must be 16-byte aligned", who);
     if (((uintptr_t)p.out & 15) || (p.out_row_stride & 7)) GB_REFUSE("%s: output rows must be 16-byte aligned", who);
     if (((uintptr_t)p.k_plane & 15) || ((uintptr_t)p.v_plane & 15)) GB_REFUSE("%s: cache planes must be 16-byte aligned", who);
@@ -623,7 +633,7 @@ static int launch_tc5(const SigmoidAttnParams& p, int rows, int pages, int sigmo
     CUtensorMap map_q, map_k, map_v;
     if (int rc = make_map(&map_q, p.q, rows, p.heads * HD, p.q_row_stride, BQ)) return rc;
     if (int rc = make_map(&map_k, p.k_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
-    if (int rc = make_map(&map_v, p.v_plane, (int64_t)pages * p.kv_heads * 64, HD, HD, 64)) return rc;
+    if (int rc = make_map(&map_v, p.v_plane, (int64_t)pages * (p.v_share > 1 ? p.kv_heads / p.v_share : p.kv_heads) * 64, HD, HD, 64)) return rc;
     dim3 grid(p.heads, ceil_div(p.max_q_len, GROUPS * BQ), p.nseq);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("%s: grid (%u, %u, %u) exceeds one launch", who, grid.x, grid.y, grid.z);
     // keys and values of the longest prompt, all kv heads: more than 48 MB do not stay in L2 beside the rest

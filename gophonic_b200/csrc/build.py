@@ -53,6 +53,7 @@ SOURCES = [
     "hyper.cu",
     "moe.cu",
     "postnorm.cu",
+    "attention_latent.cu",
     "sampling.cu",
     "no_alloc.cu",
     "dispatch.cu",

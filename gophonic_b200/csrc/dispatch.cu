@@ -134,7 +134,7 @@ GB_API int gb_gemm_add_accepts(const void* A, int a_dtype, const void* W, int w_
 
 // ------------------------------------------------------------------------------------------
 // attention
-enum GbAttnAlgo : int { GB_ATTN_SIMT = 0, GB_ATTN_DECODE_MMA = 1, GB_ATTN_PREFILL_MMA = 2, GB_ATTN_PREFILL_TC5 = 3 };
+enum GbAttnAlgo : int { GB_ATTN_SIMT = 0, GB_ATTN_DECODE_MMA = 1, GB_ATTN_PREFILL_MMA = 2, GB_ATTN_PREFILL_TC5 = 3, GB_ATTN_LATENT_MMA = 4 };
 
 GB_API int gb_attention_algo(const AttnParams* p, int dtype) {
     const AttnParamsX x = gb_attn_widen(*p);
@@ -142,9 +142,10 @@ GB_API int gb_attention_algo(const AttnParams* p, int dtype) {
 }
 
 GB_API int gb_attention_algo_x(const AttnParamsX* p, int dtype) {
+    if (gb_attention_latent_accepts(p, dtype)) return GB_ATTN_LATENT_MMA;   // one wide key head whose first channels are the values
     if (dtype != GB_BF16 || (p->d & 15) || !(p->d <= 128 || p->d == 256)) return GB_ATTN_SIMT;
     if (p->dv && p->dv != p->d) return GB_ATTN_SIMT;   // values of another size than keys: the CUDA-core kernel only
-    if (p->chunk > 0 || p->v_share > 1 || p->v_row_stride > 0) return GB_ATTN_SIMT;   // blocks of positions, shared or strided values
+    if (p->v_row_stride > 0) return GB_ATTN_SIMT;   // a value plane that is a view of wider rows
     if (p->max_q_len == 1) return GB_ATTN_DECODE_MMA;
     if (p->max_q_len >= TC5_ATTENTION_MIN_ROWS && p->d == 128 && !((uintptr_t)p->q & 15) && !(p->q_row_stride & 7) && !(p->out_row_stride & 7))
         return GB_ATTN_PREFILL_TC5;

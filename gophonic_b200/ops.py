@@ -521,7 +521,7 @@ def checked_status():
     found out of bounds since the last call (the access was skipped or redirected, nothing faulted).
     Always None in the ordinary build, whose kernels carry no checks.  Synchronises."""
     out = (c_int * 4)()
-    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid", "hyper", "postnorm"):
+    for name in ("rows", "cache", "attention_simt", "attention_mma", "attention_tc5", "linear_state", "delta_state", "attention_sigmoid", "hyper", "postnorm", "attention_latent"):
         code = int(getattr(_lib, "gb_checked_status_" + name)(out))
         if code or out[3]:
             return name, _CHECK_NAMES.get(code, f"code {code}"), out[1], out[2], out[3]
@@ -706,7 +706,7 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
     p = _attn_params(q, out, k_plane, v_plane, block_table, seq_slot, seq_q_start, seq_q_len, seq_kv_len, nseq, max_q_len,
                      heads, kv_heads, head_dim, scale, window, num_splits, scratch, value_dim, keep_first, sink, sinks, chunk, v_share)
     if algo == "auto":   # the library's own rule (head size, rows per sequence, alignment)
-        algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5")[int(_lib.gb_attention_algo_x(byref(p), _code(q.dtype)))]
+        algo = ("simt", "decode_mma", "prefill_mma", "prefill_tc5", "latent_mma")[int(_lib.gb_attention_algo_x(byref(p), _code(q.dtype)))]
     nk = 2 if num_splits > 1 else 1
     if algo == "simt":
         _check(_lib.gb_attention_simt_x(byref(p), _code(q.dtype), _stream()), nk)
@@ -716,6 +716,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane
         _check(_lib.gb_attention_prefill_mma_x(byref(p), _stream()))
     elif algo == "prefill_tc5":
         _check(_lib.gb_attention_prefill_tc5_x(byref(p), c_int(q.shape[0]), c_int(k_plane.shape[0]), _stream()))
+    elif algo == "latent_mma":
+        _check(_lib.gb_attention_latent_mma(byref(p), _stream()), nk)
     else:
         raise KernelError(f"attention: unknown algorithm '{algo}'")
     return algo

@@ -79,8 +79,10 @@ def rotate(x, positions, freqs, layout: str):
 # ---- masks and softmax attention -----------------------------------------------------------------
 def visible(kind: str, size: int, T: int) -> np.ndarray:
     """[T, T] booleans: may row i see key j.  "chunk": j <= i in the same block of ``size`` positions counted
-    from 0; "window": 0 <= i - j < size."""
+    from 0; "window": 0 <= i - j < size; ``size`` None: every j <= i."""
     i, j = np.arange(T)[:, None], np.arange(T)[None, :]
+    if size is None:
+        return j <= i
     if kind == "chunk":
         return (j <= i) & (i // size == j // size)
     return (j <= i) & (i - j < size)
@@ -101,17 +103,18 @@ def differential_lambda(w, p, diff):
 
 def differential_attention(h, w, p, m, eps):
     T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    H, d = m["heads"], m["dim"]
+    G, dv = m.get("kv_heads", H), m.get("vdim", d)
     q = (h @ w[p + "q"].T).reshape(T, H * 2, d)        # head by head, [map 1, map 2]
     k = (h @ w[p + "k"].T).reshape(T, G * 2, d)
     v = (h @ w[p + "v"].T).reshape(T, G, dv)
     q = unit_rms(q, eps) * w[p + "q.norm"]
     k = unit_rms(k, eps) * w[p + "k.norm"]
-    rot = m["rot"]
-    f = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
-    pos = np.arange(T)
-    q, k = rotate(q, pos, f, "half"), rotate(k, pos, f, "half")
-    mask = visible("chunk", m["mask"]["size"], T)
+    rot = m.get("rot")
+    if rot and rot["dims"] > 0:
+        f = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
+        q, k = rotate(q, np.arange(T), f, "half"), rotate(k, np.arange(T), f, "half")
+    mask = visible("chunk", m["mask"]["size"] if "mask" in m else None, T)
     lam = differential_lambda(w, p, m["diff"])
     out = np.zeros((T, H, dv))
     for hd in range(H):
@@ -124,18 +127,21 @@ def differential_attention(h, w, p, m, eps):
 
 def latent_attention(h, w, p, m, eps):
     T = h.shape[0]
-    H, d, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+    H, d, dr, R = m["heads"], m["dim"], m["rot_dim"], m["kv_rank"]
+    dv = m.get("vdim", d)
     cq = unit_rms(h @ w[p + "dq"].T, eps) * w[p + "dq.norm"]
     q = (cq @ w[p + "uq"].T).reshape(T, H, d + dr)
     ckv = h @ w[p + "dkv"].T
     c = unit_rms(ckv[:, :R], eps) * w[p + "dkv.norm"]
-    f = rotary_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
-    pos = np.arange(T)
-    k_rot = rotate(ckv[:, R:].reshape(T, 1, dr), pos, f, "pairs")[:, 0]
-    q_rot = rotate(q[:, :, d:], pos, f, "pairs")
+    k_rot, q_rot = ckv[:, R:], q[:, :, d:]
+    if dr > 0:
+        f = rotary_frequencies(m["rot"]["dims"], m["rot"]["base"], m["rot"].get("scaling"))
+        pos = np.arange(T)
+        k_rot = rotate(k_rot.reshape(T, 1, dr), pos, f, "pairs")[:, 0]
+        q_rot = rotate(q_rot, pos, f, "pairs")
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, d)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
-    mask = visible("window", m["mask"]["size"], T)
+    mask = visible("window", m["mask"]["size"] if "mask" in m else None, T)
     out = np.zeros((T, H, dv))
     for hd in range(H):
         qq = np.concatenate([q[:, hd, :d], q_rot[:, hd]], axis=-1)
@@ -181,8 +187,8 @@ def mixture(h, w, p, mlp):
 
 # ---- the model -----------------------------------------------------------------------------------
 def forward(cfg: dict, w: Dict[str, np.ndarray], tokens, return_layers: bool = False):
-    eps, mult = cfg["norm"]["eps"], cfg["residual_mult"]
-    x = w["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
+    eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
+    x = w["embed"][np.asarray(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     after = []
     for i, L in enumerate(cfg["layers"]):
         p = f"l{i}."
@@ -205,9 +211,10 @@ def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
         p, m = f"l{i}.", L["mixer"]
         out[p + "norm1"] = (W,)
         out[p + "ls1"] = (W,)
-        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        H, d = m["heads"], m["dim"]
+        dv = m.get("vdim", d)
         if L["type"] == "attention":
-            G = m["kv_heads"]
+            G = m.get("kv_heads", H)
             out.update({p + "mix.q": (H * 2 * d, W), p + "mix.k": (G * 2 * d, W), p + "mix.v": (G * dv, W), p + "mix.q.norm": (d,),
                         p + "mix.k.norm": (d,), p + "mix.lq1": (d,), p + "mix.lk1": (d,), p + "mix.lq2": (d,), p + "mix.lk2": (d,),
                         p + "mix.o": (W, H * dv)})
