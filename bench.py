@@ -282,13 +282,15 @@ def further_model_points(name, steps, torch, ops, hbm_peak, tflops_peak):
 # ---- another design beside its closest model ---------------------------------------------------
 # the same width, heads, head size, feed-forward and vocabulary (a Vepitar configuration beside the Pugalix one of its width:
 # both mix matrix-state layers with windowed attention; a Kalonex configuration, all attention and gated feed-forwards,
-# beside the Qwen3-shaped one of its width)
+# beside the Qwen3-shaped one of its width; a Kimilix configuration, windowed attention and mixtures with a shared expert,
+# beside the Kalonex one of its width)
 DESIGN_TWINS = {"pugalix-2k": "1.7b", "pugalix-4k": "8b", "vepitar-2k": "pugalix-2k", "vepitar-4k": "pugalix-4k",
-                "kalonex-2k": "1.7b", "kalonex-4k": "8b"}
+                "kalonex-2k": "1.7b", "kalonex-4k": "8b", "kimilix-2k": "kalonex-2k", "kimilix-4k": "kalonex-4k"}
 OP_CLASSES = ("gemm", "gemm_add", "gemm_swiglu", "gemm_scaled", "gemm_residual", "attention", "attention_decode_rope",
               "qk_norm_rope_kv_write", "state_scan", "head_norm_gate", "gla_decay", "add_rmsnorm", "embed_gather", "swiglu",
               "prenorm_layer_forward", "embed_streams", "delta_scan", "conv_qkv", "attention_sigmoid", "hyper_mix_norm", "moe_route", "moe_act", "moe_rows",
-              "moe_rows_grouped", "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_", "add_bias", "concat_cast", "add_rows", "gemm_w_cols", "gemm_grouped")
+              "moe_rows_grouped", "moe_group", "moe_gather", "moe_combine", "relu2", "tanh_", "add_bias", "concat_cast", "add_rows", "gemm_w_cols", "gemm_grouped",
+              "norm_scale_add", "diff_combine", "add_rows_gated", "latent_prep", "latent_q_rot", "head_gemm", "head_gemm_mma", "f32_to_bf16")
 
 
 class OpTimer:
@@ -577,6 +579,41 @@ def probe(name, **opts):
             work, unit = 4.0 * heads * d * seen, "TFLOP/s"
         else:
             work, unit = 2.0 * nseq * kvh * (window + 64) * d * 2, "GB/s"
+    elif name in ("attn_latent_prefill", "attn_latent_decode_b64", "attn_diff_prefill", "attn_diff_decode_b64"):
+        # latent attention: 16 heads over one key head of 512 + 64 channels whose first 512 are the values, window 1024;
+        # differential attention: 8 heads of two maps of 128 over 2 key groups, values of 128 shared by a group's two maps,
+        # blocks of 2048 positions; a prompt of 2048 tokens, or one token for each of 64 sequences
+        from gophonic_b200.parts.attention import choose_splits
+        latent, prompt = "latent" in name, name.endswith("prefill")
+        nseq, q_len, kv_len = (1, 2048, 2048) if prompt else (64, 1, 2048)
+        pages_per = (kv_len + 63) // 64
+        n_pages = nseq * pages_per
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).reshape(nseq, pages_per)
+        ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        slot, start = ints(list(range(nseq))), ints([i * q_len for i in range(nseq)])
+        ql, kl = ints([q_len] * nseq), ints([kv_len] * nseq)
+        if latent:
+            heads, kvh, d, dv, window, chunk, share = 16, 1, 576, 512, 1024, 0, 1
+            k = rnd(n_pages, 1, 64, d)
+            v = k[..., :dv]
+            seen_keys, key_bytes = window, d * 2
+        else:
+            heads, kvh, d, dv, window, chunk, share = 16, 4, 128, 128, 0, 2048, 2
+            k, v = rnd(n_pages, kvh, 64, d), rnd(n_pages, kvh // share, 64, dv)
+            seen_keys, key_bytes = kv_len, (kvh * d + kvh // share * dv) * 2
+        q = rnd(nseq * q_len, heads * d, scale=0.3)
+        out = torch.empty((nseq * q_len, heads * dv), dtype=bf, device=dev)
+        splits = 1 if q_len > 1 else choose_splits(nseq * kvh, seen_keys, 74 if latent else 148, 64 * (d + (0 if latent else dv)) * 2)
+        scratch = torch.empty(ops.attention_scratch_floats(nseq, heads, dv, splits), dtype=torch.float32, device=dev) if splits > 1 else None
+
+        def fn():
+            ops.attention(q, out, k, v, table, slot, start, ql, kl, nseq, q_len, heads, kvh, d, d ** -0.5, window, splits, scratch,
+                          value_dim=dv, chunk=chunk, v_share=share)
+        if prompt:
+            seen = sum(min(i + 1, seen_keys) for i in range(q_len))
+            work, unit = 2.0 * heads * (d + dv) * seen, "TFLOP/s"
+        else:
+            work, unit = float(nseq) * (seen_keys + 64) * key_bytes, "GB/s"
     elif name in ("prefill_step", "decode_step"):
         # a whole engine step of a 4-layer model with the layer sizes of the benchmark (or of --model):
         # the launch list of a profiler then shows every kernel of a layer with its share.  --batch

@@ -345,5 +345,9 @@ GB_API int gb_latent_prep(const void* lat, int64_t lat_stride, void* cq, const f
                           int max_slots, int dtype, cudaStream_t stream);
 GB_API int gb_latent_q_rot(const void* q, int64_t q_stride, void* out, int64_t out_stride, int rows, int heads, int d, int rot, int out_head,
                            const float* cos_t, const float* sin_t, int table_positions, const int* row_pos, int dtype, cudaStream_t stream);
+GB_API int gb_head_gemm_mma_accepts(const void* a, int64_t a_row_stride, int64_t a_head_stride, const void* w, const void* out, int64_t o_row_stride,
+                                    int64_t o_head_stride, int K, int N);
+GB_API int gb_head_gemm_mma(const void* a, int64_t a_row_stride, int64_t a_head_stride, const void* w, void* out, int64_t o_row_stride,
+                            int64_t o_head_stride, int rows, int heads, int K, int N, cudaStream_t stream);
 GB_API int gb_head_gemm(const void* a, int64_t a_row_stride, int64_t a_head_stride, const void* w, void* out, int64_t o_row_stride,
                         int64_t o_head_stride, int rows, int heads, int K, int N, int dtype, int w_dtype, cudaStream_t stream);

@@ -2,12 +2,13 @@
 // first dv channels are also the values (AttnParamsX.v_row_stride == d: the value plane is a view of the key plane), with
 // key heads much wider than a usual head (a latent of 512 and 64 rotated channels).  Prompts, portions and single tokens.
 //
-// A CTA of four warps owns 16 rows, which are (query position, head) pairs of one sequence, and walks the cache pages its
-// rows can see, one page of 64 keys a step, double-buffered with cp.async; a page is staged ONCE and serves as keys and as
-// values.  The work of a step is dealt twice: for the scores each warp takes 16 of the 64 keys (Q K^T over all d channels);
-// after the row maxima have met in shared memory every warp writes its probabilities (bf16) into a shared 16 x 64 tile;
-// for the second product each warp takes a quarter of the dv value columns (P V over all 64 keys), so a warp's float32
-// accumulators are 16 x dv / 4.  Scores, maxima, sums and accumulators are float32; masks (causal, window, blocks of
+// A CTA owns 16 or 32 rows (one or two groups of 16, four warps a group), which are (query position, head) pairs of one
+// sequence, and walks the cache pages its rows can see, one page of 64 keys a step, double-buffered with cp.async; a page
+// is staged ONCE, serves as keys and as values, and is shared by the row groups.  The work of a step is dealt twice inside
+// a group: for the scores each warp takes 16 of the 64 keys (Q K^T over all d channels, in four independent chains of
+// products so that no product waits for the one before it); after the row maxima have met in shared memory every warp
+// writes its probabilities (bf16) into the group's 16 x 64 tile; for the second product each warp takes a quarter of the
+// dv value columns (P V over all 64 keys), so a warp's float32 accumulators are 16 x dv / 4.  Scores, maxima, sums and accumulators are float32; masks (causal, window, blocks of
 // positions) come from absolute positions and tiles start at multiples of 64, so a row's result does not depend on how its
 // sequence was cut into steps or on what else the batch holds.  Single-token steps may cut the keys into splits that a
 // merge kernel joins (the same scratch layout as the other attention kernels).
@@ -24,19 +25,30 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
-constexpr int LROWS = 16, LKT = 64, LPS = LKT + 8;
+constexpr int GB_KEYS = 64;      // keys a cache page holds
+constexpr int PAGE_LIST = 512;     // tiles whose pages a CTA looks up ahead (32768 keys); beyond them, tile by tile
 
-template <int NT>   // value columns a warp owns, in tiles of 8: dv = 32 * NT
-__global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
+// NT: value columns a warp owns, in tiles of 8; RG: groups of 16 rows a CTA holds; WG: warps a group has (4 or 8), which
+// split a page's 64 keys for the scores and the dv = 8 * NT * WG value columns for the second product
+// LKT: keys a step stages (a page, or half a page); STAGES: steps staged at a time.
+template <int NT, int RG, int WG, int LKT, int STAGES>
+__global__ void __launch_bounds__(32 * WG * RG) attn_latent_mma_kernel(AttnParamsX p) {
+    constexpr int LROWS = 16 * RG, THREADS = 32 * WG * RG, LPS = LKT + 8;
+    constexpr int KW = LKT / WG, J = KW / 8;      // keys a warp scores, in tiles of 8
     const int d = p.d, SD = d + 8, KS = d / 16;
-    constexpr int DV = 32 * NT;
+    constexpr int DV = 8 * NT * WG;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);          // [16][SD]
-    bf16* Ks = Qs + LROWS * SD;                            // [2][64][SD]
-    bf16* Ps = Ks + 2 * LKT * SD;                          // [16][72]
-    float* red = reinterpret_cast<float*>(Ps + LROWS * LPS);   // [4 warps][16 rows]
+    bf16* Ks = Qs + LROWS * SD;                            // [STAGES][LKT][SD]
+    bf16* Ps_all = Ks + STAGES * LKT * SD;                 // [RG][16][LKT + 8]
+    float* red_all = reinterpret_cast<float*>(Ps_all + LROWS * LPS);   // [RG][WG warps][16 rows]
+    __shared__ int page_list[PAGE_LIST];
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int tid = threadIdx.x, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int rg = (tid >> 5) / WG, warp = (tid >> 5) % WG;      // row group, and the warp's place inside it
+    bf16* Ps = Ps_all + rg * 16 * LPS;
+    float* red = red_all + rg * (16 * WG);
+    const bf16* Qg = Qs + rg * 16 * SD;
     const int H = p.heads;
     const int HC = H < LROWS ? H : LROWS;       // heads a CTA holds
     const int QT = LROWS / HC;                  // query positions a CTA holds
@@ -54,7 +66,7 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
     bool rok[2];
 #pragma unroll
     for (int e = 0; e < 2; e++) {
-        const int r = g + 8 * e;
+        const int r = rg * 16 + g + 8 * e;
         const int qi = r / HC, hd = h0 + r % HC;
         rok[e] = qi < QT && q0 + qi < q_len && hd < H;
         rq[e] = q0 + qi;
@@ -80,17 +92,19 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
     const int n = my_hi > my_lo ? my_hi - my_lo : 0;
 
     const int CH = d / 8;     // 16-byte pieces of a row
+    // the physical pages of this CTA's tiles, looked up once: a tile's copies are then issued without waiting for the block table
+    for (int i = tid; i < n && i < PAGE_LIST; i += THREADS) page_list[i] = (int)page_of(bt, (my_lo + i) * LKT, p.bt_stride, p.pages);
+    __syncthreads();
     auto load_tile = [&](int i) {
-        const int64_t page = page_of(bt, (my_lo + i) * LKT, p.bt_stride, p.pages);
-        const bf16* src = (const bf16*)p.k_plane + page * LKT * (int64_t)d;
-        bf16* st = Ks + (i & 1) * LKT * SD;
-        for (int idx = tid; idx < LKT * CH; idx += 128) {
-            const int key = idx / CH, c = idx - key * CH;
-            cp_async16(st + key * SD + c * 8, src + (int64_t)key * d + c * 8, 16);
-        }
+        const int64_t page = i < PAGE_LIST ? page_list[i] : page_of(bt, (my_lo + i) * LKT, p.bt_stride, p.pages);
+        const bf16* src = (const bf16*)p.k_plane + (page * GB_KEYS + ((my_lo + i) * LKT) % GB_KEYS) * (int64_t)d;
+        bf16* st = Ks + (i % STAGES) * LKT * SD;
+        // a warp copies whole rows, its lanes the row's 16-byte pieces
+        for (int key = tid >> 5; key < LKT; key += THREADS / 32)
+            for (int c = lane; c < CH; c += 32) cp_async16(st + key * SD + c * 8, src + (int64_t)key * d + c * 8, 16);
     };
     {
-        for (int idx = tid; idx < LROWS * CH; idx += 128) {
+        for (int idx = tid; idx < LROWS * CH; idx += THREADS) {
             const int r = idx / CH, c = idx - r * CH;
             const int qi = r / HC, hd = h0 + r % HC;
             const bool ok = qi < QT && q0 + qi < q_len && hd < H;
@@ -99,6 +113,11 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
         }
         if (n > 0) load_tile(0);
         cp_async_commit();
+#pragma unroll
+        for (int u = 1; u < STAGES - 1; u++) {
+            if (u < n) load_tile(u);
+            cp_async_commit();
+        }
     }
 
     const float sc = p.scale * LOG2E;
@@ -110,31 +129,55 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
         for (int e = 0; e < 4; e++) o[j][e] = 0.f;
 
     for (int i = 0; i < n; i++) {
-        cp_async_wait<0>();
+        cp_async_wait<STAGES - 2>();
         __syncthreads();                       // tile i has landed; everyone is done with tile i - 1, the probabilities and the maxima
-        if (i + 1 < n) load_tile(i + 1);
+        if (i + STAGES - 1 < n) load_tile(i + STAGES - 1);
         cp_async_commit();
-        const bf16* kt = Ks + (i & 1) * LKT * SD;
+        const bf16* kt = Ks + (i % STAGES) * LKT * SD;
         const int t = my_lo + i;
-        // scores of this warp's 16 keys
-        float s[2][4];
+        // scores of this warp's keys: four chains of products over the channels (steps ks, ks + 1, ks + 2, ks + 3), added up
+        // in a fixed order
+        float s[J][4], part[3][J][4];
 #pragma unroll
-        for (int j = 0; j < 2; j++)
+        for (int j = 0; j < J; j++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) s[j][e] = 0.f;
-        for (int ks = 0; ks < KS; ks++) {
-            uint32_t a[4], b[4];
-            ldmatrix_x4(a, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * SD + ks * 16 + (lane >> 4) * 8);
-            ldmatrix_x4(b, kt + (warp * 16 + (lane & 7) + (lane >> 4) * 8) * SD + ks * 16 + ((lane >> 3) & 1) * 8);
-            mma_bf16_16816(s[0], a[0], a[1], a[2], a[3], b[0], b[1]);
-            mma_bf16_16816(s[1], a[0], a[1], a[2], a[3], b[2], b[3]);
+            for (int e = 0; e < 4; e++) s[j][e] = part[0][j][e] = part[1][j][e] = part[2][j][e] = 0.f;
+        const bf16* qa = Qg + ((lane & 7) + ((lane >> 3) & 1) * 8) * SD + (lane >> 4) * 8;
+        // 16 keys: four 8 x 8 pieces (keys 0-7 and 8-15, channels 0-7 and 8-15); 8 keys: two pieces, addressed by lanes 0-15
+        const bf16* kb = J == 2 ? kt + (warp * KW + (lane & 7) + (lane >> 4) * 8) * SD + ((lane >> 3) & 1) * 8
+                                : kt + (warp * KW + (lane & 7)) * SD + ((lane >> 3) & 1) * 8;
+        auto products = [&](float (&acc)[J][4], int step) {
+            uint32_t a[4];
+            ldmatrix_x4(a, qa + step * 16);
+            if (J == 2) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kb + step * 16);
+                mma_bf16_16816(acc[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+                mma_bf16_16816(acc[J - 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+            } else {
+                uint32_t b[2];
+                ldmatrix_x2(b, kb + step * 16);
+                mma_bf16_16816(acc[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+            }
+        };
+        int ks = 0;
+        for (; ks + 3 < KS; ks += 4) {
+            products(s, ks);
+            products(part[0], ks + 1);
+            products(part[1], ks + 2);
+            products(part[2], ks + 3);
         }
+        for (; ks < KS; ks++) products(s, ks);
+#pragma unroll
+        for (int j = 0; j < J; j++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s[j][e] = (s[j][e] + part[0][j][e]) + (part[1][j][e] + part[2][j][e]);
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
+        for (int j = 0; j < J; j++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                const int key = t * LKT + warp * 16 + j * 8 + t4 * 2 + (e & 1);
+                const int key = t * LKT + warp * KW + j * 8 + t4 * 2 + (e & 1);
                 const int w = e >> 1;
                 const int pos = rpos[w];
                 const bool ok = rok[w] && key <= pos && (p.window <= 0 || key > pos - p.window) && (p.chunk <= 0 || key >= pos - pos % p.chunk);
@@ -148,14 +191,17 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         if (t4 == 0) {
-            red[warp * LROWS + g] = mx0;
-            red[warp * LROWS + g + 8] = mx1;
+            red[warp * 16 + g] = mx0;
+            red[warp * 16 + g + 8] = mx1;
         }
         __syncthreads();
-        mx0 = fmaxf(fmaxf(red[g], red[LROWS + g]), fmaxf(red[2 * LROWS + g], red[3 * LROWS + g]));
-        mx1 = fmaxf(fmaxf(red[g + 8], red[LROWS + g + 8]), fmaxf(red[2 * LROWS + g + 8], red[3 * LROWS + g + 8]));
-        mx0 = fmaxf(mx0, m0);
-        mx1 = fmaxf(mx1, m1);
+        mx0 = m0;
+        mx1 = m1;
+#pragma unroll
+        for (int ww = 0; ww < WG; ww++) {
+            mx0 = fmaxf(mx0, red[ww * 16 + g]);
+            mx1 = fmaxf(mx1, red[ww * 16 + g + 8]);
+        }
         const float base0 = mx0 == -INFINITY ? 0.f : mx0, base1 = mx1 == -INFINITY ? 0.f : mx1;
         const float c0 = exp2f(m0 - base0), c1 = exp2f(m1 - base1);
         m0 = mx0;
@@ -170,11 +216,11 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
             o[j][3] *= c1;
         }
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
+        for (int j = 0; j < J; j++) {
             const float p0 = exp2f(s[j][0] - base0), p1 = exp2f(s[j][1] - base0), p2 = exp2f(s[j][2] - base1), p3 = exp2f(s[j][3] - base1);
             l0 += p0 + p1;
             l1 += p2 + p3;
-            const int col = warp * 16 + j * 8 + t4 * 2;
+            const int col = warp * KW + j * 8 + t4 * 2;
             *reinterpret_cast<uint32_t*>(Ps + g * LPS + col) = pack_bf16(p0, p1);
             *reinterpret_cast<uint32_t*>(Ps + (g + 8) * LPS + col) = pack_bf16(p2, p3);
         }
@@ -200,12 +246,16 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     __syncthreads();
     if (t4 == 0) {
-        red[warp * LROWS + g] = l0;
-        red[warp * LROWS + g + 8] = l1;
+        red[warp * 16 + g] = l0;
+        red[warp * 16 + g + 8] = l1;
     }
     __syncthreads();
-    const float L0 = red[g] + red[LROWS + g] + red[2 * LROWS + g] + red[3 * LROWS + g];
-    const float L1 = red[g + 8] + red[LROWS + g + 8] + red[2 * LROWS + g + 8] + red[3 * LROWS + g + 8];
+    float L0 = 0.f, L1 = 0.f;
+#pragma unroll
+    for (int ww = 0; ww < WG; ww++) {      // in warp order
+        L0 += red[ww * 16 + g];
+        L1 += red[ww * 16 + g + 8];
+    }
 #pragma unroll
     for (int e = 0; e < 2; e++) {
         if (!rok[e]) continue;
@@ -230,21 +280,24 @@ __global__ void __launch_bounds__(128) attn_latent_mma_kernel(AttnParamsX p) {
     }
 }
 
-template <int NT>
+template <int NT, int RG, int WG, int LKT, int STAGES>
 int launch_latent(const AttnParamsX& p, cudaStream_t stream) {
+    constexpr int LPS = LKT + 8;
+    constexpr int LROWS = 16 * RG;
     const int HC = p.heads < LROWS ? p.heads : LROWS, QT = LROWS / HC;
     dim3 grid(ceil_div(p.max_q_len, QT), ceil_div(p.heads, HC), p.nseq * p.num_splits);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("attention_latent: grid (%u, %u, %u) exceeds one launch", grid.x, grid.y, grid.z);
-    const size_t smem = ((size_t)(LROWS + 2 * LKT) * (p.d + 8) + (size_t)LROWS * LPS) * sizeof(bf16) + 4 * LROWS * sizeof(float);
-    static size_t configured = 0;
-    if (smem > configured && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attn_latent_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    const size_t smem = ((size_t)(LROWS + STAGES * LKT) * (p.d + 8) + (size_t)LROWS * LPS) * sizeof(bf16) + WG * LROWS * sizeof(float);
+    if (smem > 220 * 1024 - PAGE_LIST * sizeof(int)) GB_REFUSE("attention_latent: keys of %d channels exceed what one CTA stages", p.d);
+    static size_t configured = 0;      // always opted in: the static page list counts towards the 48 KB a kernel has without
+    if (configured == 0) {
+        cudaError_t e = cudaFuncSetAttribute(attn_latent_mma_kernel<NT, RG, WG, LKT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) GB_REFUSE("attention_latent: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         configured = 220 * 1024;
     }
-    attn_latent_mma_kernel<NT><<<grid, 128, smem, stream>>>(p);
+    attn_latent_mma_kernel<NT, RG, WG, LKT, STAGES><<<grid, 32 * WG * RG, smem, stream>>>(p);
     GB_CHECK_LAUNCH("attention_latent");
-    if (p.num_splits > 1) return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, 32 * NT, p.num_splits, 0, nullptr, stream);
+    if (p.num_splits > 1) return gb_attention_merge_launch(p.scratch, p.out, GB_BF16, p.out_row_stride, p.seq_q_start, p.nseq, p.heads, 8 * NT * WG, p.num_splits, 0, nullptr, stream);
     return 0;
 }
 
@@ -265,11 +318,16 @@ GB_API int gb_attention_latent_mma(const AttnParamsX* pp, cudaStream_t stream) {
     if (!gb_attention_latent_accepts(&p, GB_BF16)) GB_REFUSE("attention_latent: %d heads over %d key heads of %d with values of %d are not what this kernel takes", p.heads, p.kv_heads, p.d, p.dv);
     if (p.num_splits < 1 || (p.num_splits > 1 && (p.max_q_len != 1 || !p.scratch))) GB_REFUSE("attention_latent: %d key splits", p.num_splits);
     if (p.window < 0 || p.chunk < 0) GB_REFUSE("attention_latent: window %d, blocks of %d", p.window, p.chunk);
-    switch ((p.dv ? p.dv : p.d) / 32) {
-        case 2: return launch_latent<2>(p, stream);
-        case 4: return launch_latent<4>(p, stream);
-        case 8: return launch_latent<8>(p, stream);
-        default: return launch_latent<16>(p, stream);
+    // two groups of rows share a staged page where a sequence brings that many (query position, head) pairs; a single group
+    // (single tokens of up to 16 heads) gets eight warps, two a scheduler, where its value heads are wide enough to deal out.
+    // (Half pages staged four deep, <.., 1, 4, 32, 4>, measured slower for single tokens: 65 against 54 us for 64 sequences of
+    // 16 heads over 1024 keys of 576: the step is bound by its products, not by the copies.)
+    const bool two = (int64_t)p.max_q_len * p.heads > 16;
+    switch ((p.dv ? p.dv : p.d) / 64) {
+        case 1: return two ? launch_latent<2, 2, 4, 64, 2>(p, stream) : launch_latent<2, 1, 4, 64, 2>(p, stream);
+        case 2: return two ? launch_latent<4, 2, 4, 64, 2>(p, stream) : launch_latent<2, 1, 8, 64, 2>(p, stream);
+        case 4: return two ? launch_latent<8, 2, 4, 64, 2>(p, stream) : launch_latent<4, 1, 8, 64, 2>(p, stream);
+        default: return two ? launch_latent<16, 2, 4, 64, 2>(p, stream) : launch_latent<8, 1, 8, 64, 2>(p, stream);
     }
 }
 

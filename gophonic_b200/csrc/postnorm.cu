@@ -11,11 +11,13 @@
 //                   the key part (neighbouring channels turn together), both into the key plane at the row's position.
 // latent_q_rot:     the rotated channels of every query head, rotated and copied behind the head's absorbed channels.
 // head_gemm:        out[r, h, :] = a[r, h, :] W_h for every head h in one launch, W [heads, K, N]; float32 sums.
+// head_gemm_mma:    the same for many bfloat16 rows on the tensor cores, W [heads, N, K].
 //
 // Everything is computed in float32 whatever the activation dtype; a row's result depends on that row alone and the
 // order of every sum is fixed by the row's width.
 #include "api.h"
 #include "common.cuh"
+#include "mma.cuh"
 
 #include <math.h>
 
@@ -180,35 +182,128 @@ __global__ void latent_q_rot_kernel(const T* __restrict__ q, int64_t q_stride, T
     }
 }
 
-// out[r, h, n] = sum_k a[r, h, k] W[h, k, n]: a CTA takes 8 rows of one head and 128 columns; the rows are staged as float32,
-// a thread owns one column, W is read along n (whole lines a warp).
-constexpr int HG_ROWS = 8;
+// out[r, h, n] = sum_k a[r, h, k] W[h, k, n] for few rows: a CTA of eight warps takes 8 rows of one head and 32 columns; the
+// rows are staged as float32, a lane owns one column, the warps split K (eight loads of W in flight a lane, along n whole
+// segments a warp) and their sums meet in shared memory, added in warp order.
+constexpr int HG_ROWS = 8, HG_WARPS = 8, HG_COLS = 32;
 
 template <typename T, typename TW>
-__global__ void __launch_bounds__(128) head_gemm_kernel(const T* __restrict__ a, int64_t a_row_stride, int64_t a_head_stride, const TW* __restrict__ w,
-                                                        T* __restrict__ out, int64_t o_row_stride, int64_t o_head_stride, int rows, int K, int N) {
-    extern __shared__ float as[];   // [HG_ROWS][K]
+__global__ void __launch_bounds__(32 * HG_WARPS) head_gemm_kernel(const T* __restrict__ a, int64_t a_row_stride, int64_t a_head_stride,
+                                                                 const TW* __restrict__ w, T* __restrict__ out, int64_t o_row_stride,
+                                                                 int64_t o_head_stride, int rows, int K, int N) {
+    extern __shared__ float as[];   // [HG_ROWS][K], then [HG_WARPS][HG_ROWS][HG_COLS]
+    float* red = as + HG_ROWS * K;
     const int hd = blockIdx.y;
     const int r0 = blockIdx.z * HG_ROWS;
-    const int n = blockIdx.x * 128 + threadIdx.x;
-    for (int idx = threadIdx.x; idx < HG_ROWS * K; idx += 128) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * HG_COLS + lane;
+    for (int idx = threadIdx.x; idx < HG_ROWS * K; idx += 32 * HG_WARPS) {
         const int rr = idx / K, k = idx - rr * K;
         as[idx] = r0 + rr < rows ? to_f32<T>(a[(int64_t)(r0 + rr) * a_row_stride + (int64_t)hd * a_head_stride + k]) : 0.f;
     }
     __syncthreads();
-    if (n >= N) return;
-    const TW* wp = w + (int64_t)hd * K * N + n;
+    const int per = (K + HG_WARPS - 1) / HG_WARPS;
+    const int k_lo = warp * per, k_hi = k_lo + per < K ? k_lo + per : K;
     float acc[HG_ROWS];
 #pragma unroll
     for (int rr = 0; rr < HG_ROWS; rr++) acc[rr] = 0.f;
-    for (int k = 0; k < K; k++) {
-        const float wv = to_f32<TW>(wp[(int64_t)k * N]);
+    if (n < N) {
+        const TW* wp = w + (int64_t)hd * K * N + n;
+        int k = k_lo;
+        for (; k + 7 < k_hi; k += 8) {
+            float wv[8];
 #pragma unroll
-        for (int rr = 0; rr < HG_ROWS; rr++) acc[rr] = fmaf(as[rr * K + k], wv, acc[rr]);
+            for (int u = 0; u < 8; u++) wv[u] = to_f32<TW>(wp[(int64_t)(k + u) * N]);
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+#pragma unroll
+                for (int rr = 0; rr < HG_ROWS; rr++) acc[rr] = fmaf(as[rr * K + k + u], wv[u], acc[rr]);
+        }
+        for (; k < k_hi; k++) {
+            const float wv = to_f32<TW>(wp[(int64_t)k * N]);
+#pragma unroll
+            for (int rr = 0; rr < HG_ROWS; rr++) acc[rr] = fmaf(as[rr * K + k], wv, acc[rr]);
+        }
     }
 #pragma unroll
-    for (int rr = 0; rr < HG_ROWS; rr++)
-        if (r0 + rr < rows) out[(int64_t)(r0 + rr) * o_row_stride + (int64_t)hd * o_head_stride + n] = from_f32<T>(acc[rr]);
+    for (int rr = 0; rr < HG_ROWS; rr++) red[(warp * HG_ROWS + rr) * HG_COLS + lane] = acc[rr];
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < HG_ROWS * HG_COLS; idx += 32 * HG_WARPS) {
+        const int rr = idx / HG_COLS, c = idx - rr * HG_COLS;
+        const int col = blockIdx.x * HG_COLS + c;
+        if (r0 + rr >= rows || col >= N) continue;
+        float t = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < HG_WARPS; ww++) t += red[(ww * HG_ROWS + rr) * HG_COLS + c];
+        out[(int64_t)(r0 + rr) * o_row_stride + (int64_t)hd * o_head_stride + col] = from_f32<T>(t);
+    }
+}
+
+// The same product for many rows on the tensor cores (bf16 mma.sync), W as [heads][N][K]: a CTA takes 64 rows and 64
+// columns of one head, a warp 16 of the rows; K in pieces of 64, double-buffered with cp.async.
+constexpr int HM_T = 64, HM_S = HM_T + 8;
+
+__global__ void __launch_bounds__(128) head_gemm_mma_kernel(const __nv_bfloat16* __restrict__ a, int64_t a_row_stride, int64_t a_head_stride,
+                                                            const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                                                            int64_t o_row_stride, int64_t o_head_stride, int rows, int K, int N) {
+    __shared__ __align__(16) __nv_bfloat16 As[2][HM_T][HM_S];
+    __shared__ __align__(16) __nv_bfloat16 Ws[2][HM_T][HM_S];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+    const int n0 = blockIdx.x * HM_T, hd = blockIdx.y, r0 = blockIdx.z * HM_T;
+    const __nv_bfloat16* ap = a + (int64_t)hd * a_head_stride;
+    const __nv_bfloat16* wp = w + (int64_t)hd * N * K;
+    const int chunks = (K + HM_T - 1) / HM_T;
+    auto load = [&](int c) {
+        const int buf = c & 1, k0 = c * HM_T;
+        for (int idx = tid; idx < HM_T * 8; idx += 128) {
+            const int r = idx >> 3, piece = idx & 7;
+            const int k = k0 + piece * 8;
+            const bool ka = k < K;
+            const bool oka = ka && r0 + r < rows, okw = ka && n0 + r < N;
+            cp_async16(&As[buf][r][piece * 8], oka ? ap + (int64_t)(r0 + r) * a_row_stride + k : ap, oka ? 16 : 0);
+            cp_async16(&Ws[buf][r][piece * 8], okw ? wp + (int64_t)(n0 + r) * K + k : wp, okw ? 16 : 0);
+        }
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[j][e] = 0.f;
+    load(0);
+    cp_async_commit();
+    for (int c = 0; c < chunks; c++) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (c + 1 < chunks) load(c + 1);
+        cp_async_commit();
+        const int buf = c & 1;
+#pragma unroll
+        for (int ks = 0; ks < HM_T / 16; ks++) {
+            uint32_t af[4];
+            ldmatrix_x4(af, &As[buf][warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+            for (int jp = 0; jp < 4; jp++) {
+                uint32_t b[4];
+                ldmatrix_x4(b, &Ws[buf][jp * 16 + (lane & 7) + (lane >> 4) * 8][ks * 16 + ((lane >> 3) & 1) * 8]);
+                mma_bf16_16816(acc[jp * 2], af[0], af[1], af[2], af[3], b[0], b[1]);
+                mma_bf16_16816(acc[jp * 2 + 1], af[0], af[1], af[2], af[3], b[2], b[3]);
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+        const int r = r0 + warp * 16 + g + 8 * e;
+        if (r >= rows) continue;
+        __nv_bfloat16* op = out + (int64_t)r * o_row_stride + (int64_t)hd * o_head_stride;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int col = n0 + j * 8 + t4 * 2;
+            if (col + 1 < N)
+                *reinterpret_cast<uint32_t*>(op + col) = pack_bf16(acc[j][2 * e], acc[j][2 * e + 1]);
+            else if (col < N)
+                op[col] = __float2bfloat16_rn(acc[j][2 * e]);
+        }
+    }
 }
 
 }  // namespace
@@ -290,20 +385,45 @@ GB_API int gb_head_gemm(const void* a, int64_t a_row_stride, int64_t a_head_stri
                         int64_t o_head_stride, int rows, int heads, int K, int N, int dtype, int w_dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (heads <= 0 || K <= 0 || N <= 0) GB_REFUSE("head_gemm: %d heads of %d x %d", heads, K, N);
-    const size_t smem = (size_t)HG_ROWS * K * sizeof(float);
-    if (smem > 48 * 1024) GB_REFUSE("head_gemm: rows of %d exceed what one CTA stages", K);
-    dim3 grid((N + 127) / 128, heads, (rows + HG_ROWS - 1) / HG_ROWS);
+    const size_t smem = ((size_t)HG_ROWS * K + (size_t)HG_WARPS * HG_ROWS * HG_COLS) * sizeof(float);
+    if (smem > 96 * 1024) GB_REFUSE("head_gemm: rows of %d exceed what one CTA stages", K);
+    dim3 grid((N + HG_COLS - 1) / HG_COLS, heads, (rows + HG_ROWS - 1) / HG_ROWS);
     if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("head_gemm: %d heads, %d rows exceed one launch", heads, rows);
-    if (dtype == GB_F32 && w_dtype == GB_F32)
-        head_gemm_kernel<float, float><<<grid, 128, smem, stream>>>((const float*)a, a_row_stride, a_head_stride, (const float*)w, (float*)out, o_row_stride,
-                                                                    o_head_stride, rows, K, N);
-    else if (dtype == GB_BF16 && w_dtype == GB_BF16)
-        head_gemm_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 128, smem, stream>>>((const __nv_bfloat16*)a, a_row_stride, a_head_stride,
-                                                                                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row_stride,
-                                                                                    o_head_stride, rows, K, N);
-    else
+    if (dtype == GB_F32 && w_dtype == GB_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(head_gemm_kernel<float, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        head_gemm_kernel<float, float><<<grid, 32 * HG_WARPS, smem, stream>>>((const float*)a, a_row_stride, a_head_stride, (const float*)w, (float*)out,
+                                                                             o_row_stride, o_head_stride, rows, K, N);
+    } else if (dtype == GB_BF16 && w_dtype == GB_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(head_gemm_kernel<__nv_bfloat16, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        head_gemm_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 32 * HG_WARPS, smem, stream>>>((const __nv_bfloat16*)a, a_row_stride, a_head_stride,
+                                                                                             (const __nv_bfloat16*)w, (__nv_bfloat16*)out, o_row_stride,
+                                                                                             o_head_stride, rows, K, N);
+    } else {
         GB_REFUSE("head_gemm: activations of dtype %d with weights of dtype %d", dtype, w_dtype);
+    }
     GB_CHECK_LAUNCH("head_gemm");
+    return 0;
+}
+
+// Whether the tensor-core form takes these operands: 16-byte aligned rows of a and W, even strides of the output.
+GB_API int gb_head_gemm_mma_accepts(const void* a, int64_t a_row_stride, int64_t a_head_stride, const void* w, const void* out, int64_t o_row_stride,
+                                    int64_t o_head_stride, int K, int N) {
+    return !(K & 7) && !(a_row_stride & 7) && !(a_head_stride & 7) && !((uintptr_t)a & 15) && !((uintptr_t)w & 15) && !(o_row_stride & 1) &&
+           !(o_head_stride & 1) && !((uintptr_t)out & 3) && K > 0 && N > 0;
+}
+
+// out[r, h, :] = a[r, h, :] W_h^T with W as [heads][N][K], bfloat16, on the tensor cores.
+GB_API int gb_head_gemm_mma(const void* a, int64_t a_row_stride, int64_t a_head_stride, const void* w, void* out, int64_t o_row_stride,
+                            int64_t o_head_stride, int rows, int heads, int K, int N, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (heads <= 0 || !gb_head_gemm_mma_accepts(a, a_row_stride, a_head_stride, w, out, o_row_stride, o_head_stride, K, N))
+        GB_REFUSE("head_gemm_mma: %d heads of %d x %d with these strides are not what this kernel takes", heads, K, N);
+    dim3 grid((N + HM_T - 1) / HM_T, heads, (rows + HM_T - 1) / HM_T);
+    if (grid.y > 65535 || grid.z > 65535) GB_REFUSE("head_gemm_mma: %d heads, %d rows exceed one launch", heads, rows);
+    head_gemm_mma_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, a_row_stride, a_head_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out,
+                                                   o_row_stride, o_head_stride, rows, K, N);
+    GB_CHECK_LAUNCH("head_gemm_mma");
     return 0;
 }
 

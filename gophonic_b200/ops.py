@@ -1580,7 +1580,7 @@ def latent_q_rot(q: torch.Tensor, out: torch.Tensor, heads: int, head_dim: int, 
                                 c_int(rot), c_int(out_head), _ptr(cos), _ptr(sin), c_int(cos.shape[0]), _ptr(row_pos), _code(q.dtype), _stream()))
 
 
-HEAD_GEMM_MAX_K = 1536     # float32 rows of this many channels are what one CTA of the kernel stages
+HEAD_GEMM_MAX_K = 2048     # float32 rows of this many channels are what one CTA of the kernel stages
 
 
 def head_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -1596,3 +1596,25 @@ def head_gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError(f"head_gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _check(_lib.gb_head_gemm(_ptr(a), c_int64(a.stride(0)), c_int64(a.stride(1)), _ptr(w), _ptr(out), c_int64(out.stride(0)), c_int64(out.stride(1)),
                              c_int(rows), c_int(heads), c_int(K), c_int(N), _code(a.dtype), _code(w.dtype), _stream()))
+
+
+def head_gemm_mma_accepts(a: torch.Tensor, w_nk: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether ``head_gemm_mma`` takes these operands (bfloat16, 16-byte aligned rows, even output strides)."""
+    if not (a.dtype == w_nk.dtype == out.dtype == torch.bfloat16) or a.dim() != 3 or a.stride(2) != 1 or out.stride(2) != 1:
+        return False
+    return bool(_lib.gb_head_gemm_mma_accepts(_ptr(a), c_int64(a.stride(0)), c_int64(a.stride(1)), _ptr(w_nk), _ptr(out), c_int64(out.stride(0)),
+                                              c_int64(out.stride(1)), c_int(a.shape[2]), c_int(w_nk.shape[1])))
+
+
+def head_gemm_mma(a: torch.Tensor, w_nk: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, h, :] = a[r, h, :] @ w_nk[h]^T for every head in one launch on the tensor cores: ``a`` [rows, heads, K] and
+    ``out`` [rows, heads, N] may be views with free row and head strides, ``w_nk`` is [heads, N, K]; bfloat16."""
+    _need(a, "head_gemm a", torch.bfloat16, 3, contiguous=False)
+    _need(w_nk, "head_gemm w", torch.bfloat16, 3)
+    _need(out, "head_gemm out", torch.bfloat16, 3, contiguous=False)
+    rows, heads, K = a.shape
+    N = w_nk.shape[1]
+    if w_nk.shape != (heads, N, K) or out.shape != (rows, heads, N) or a.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError(f"head_gemm_mma: a {tuple(a.shape)}, w {tuple(w_nk.shape)}, out {tuple(out.shape)}")
+    _check(_lib.gb_head_gemm_mma(_ptr(a), c_int64(a.stride(0)), c_int64(a.stride(1)), _ptr(w_nk), _ptr(out), c_int64(out.stride(0)),
+                                 c_int64(out.stride(1)), c_int(rows), c_int(heads), c_int(K), c_int(N), _stream()))

@@ -11,8 +11,8 @@ portions, single tokens and batches are one path.
 Per step: one product for both down-projections; a row-wise kernel for the two RMS norms, the rotation of k_r and the
 cache write (``ops.latent_prep``); the query up-projection; the per-head product with W_uk and the rotation of the
 queries' rotated part into the absorbed queries; attention; the per-head product with W_uv; the output projection.
-The per-head products are one launch for all heads on the CUDA cores (few rows, and float32) or one tensor-core
-product a head (prompts in bfloat16).
+The per-head products are one launch for all heads: on the CUDA cores for few rows and for float32, on the tensor cores
+(mma.sync) for prompts in bfloat16; operands that kernel cannot take run one product a head.
 """
 from __future__ import annotations
 
@@ -81,7 +81,9 @@ class LatentAttention(Mixer):
             if size > 0:
                 seen = min(seen, size)
         elem = 4 if self.rt.is_fp32 else 2
-        return choose_splits(nseq, seen, sm_count, 64 * self.key_dim * elem)
+        # a page of latents fills most of an SM's shared memory twice over: one CTA an SM, where the model of the split
+        # choice counts two
+        return choose_splits(nseq, seen, max(1, sm_count // 2), 64 * self.key_dim * elem)
 
     def key_splits(self, batch):
         s = self.spec
@@ -97,6 +99,9 @@ class LatentAttention(Mixer):
         rows, heads, K = a.shape
         if (self.rt.is_fp32 or rows <= self.ROWS_ONE_LAUNCH) and K <= ops.HEAD_GEMM_MAX_K:
             ops.head_gemm(a, w_kn, out)
+            return
+        if ops.head_gemm_mma_accepts(a, w_nk, out):
+            ops.head_gemm_mma(a, w_nk, out)
             return
         for h in range(heads):
             ops.gemm(a[:, h, :], w_nk[h], out[:, h, :])

@@ -132,12 +132,12 @@ def test_named_configurations_are_config_files_read_like_any_other():
     from gophonic_b200 import registry
     from gophonic_b200.api import ErrUnknownFormat, _parse_random, random_model_path
     from gophonic_b200.config.presets import preset, preset_names
-    assert preset_names() == ["1.7b", "32b", "8b", "kalonex-2k", "kalonex-4k", "kalonex-tiny", "pugalix-2k", "pugalix-4k", "pugalix-tiny", "tinyA", "tinyB", "vepitar-2k",
+    assert preset_names() == ["1.7b", "32b", "8b", "kalonex-2k", "kalonex-4k", "kalonex-tiny", "kimilix-2k", "kimilix-4k", "kimilix-tiny", "pugalix-2k", "pugalix-4k", "pugalix-tiny", "tinyA", "tinyB", "vepitar-2k",
                               "vepitar-4k", "vepitar-tiny"]
     for name in preset_names():
         raw = preset(name)
         cfg = registry.config_class(registry.architecture_of(raw)).from_dict(raw)
-        if name.startswith(("pugalix", "vepitar", "kalonex")):
+        if name.startswith(("pugalix", "vepitar", "kalonex", "kimilix")):
             assert cfg.to_dict() == raw
         else:
             assert cfg.to_dict()["hidden_size"] == raw["hidden_size"]

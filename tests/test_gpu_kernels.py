@@ -712,7 +712,7 @@ def test_attention_rescales_its_running_output_by_a_real_factor(ops, algo):
 
 def test_attention_refuses_what_it_cannot_take(ops):
     with pytest.raises(ops.KernelError, match="head_dim"):
-        attention_case(ops, torch.float32, 2, 1, 272, [3], [3])
+        attention_case(ops, torch.float32, 2, 1, 656, [3], [3])
     with pytest.raises(ops.KernelError, match="single-token"):
         attention_case(ops, torch.float32, 2, 1, 32, [3], [3], splits=2)
 

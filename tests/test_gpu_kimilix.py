@@ -523,6 +523,25 @@ def test_a_product_for_every_head_in_one_launch(shape, dtype):
     assert out[:, :, N:].abs().max().item() == 0.0
 
 
+@pytest.mark.parametrize("shape", [(70, 3, 16, 24), (300, 2, 128, 512), (65, 5, 72, 130), (200, 16, 512, 128), (33, 1, 136, 7)])
+def test_a_product_for_every_head_on_the_tensor_cores(shape):
+    import torch
+    from gophonic_b200 import ops
+    ops.use_device(0)
+    rows, heads, K, N = shape
+    rng = np.random.default_rng(sum(shape))
+    a = torch.tensor(rng.standard_normal((rows, heads, K + 8)), dtype=torch.float32).to(torch.bfloat16).cuda()      # a view: rows wider than K
+    w = torch.tensor(rng.standard_normal((heads, N, K)) / np.sqrt(K), dtype=torch.float32).to(torch.bfloat16).cuda()
+    out = torch.zeros((rows, heads, N + 2 + (N & 1)), dtype=torch.bfloat16, device="cuda:0")      # even strides
+    assert ops.head_gemm_mma_accepts(a[:, :, :K], w, out[:, :, :N])
+    ops.head_gemm_mma(a[:, :, :K], w, out[:, :, :N])
+    torch.cuda.synchronize()
+    want = np.einsum("rhk,hnk->rhn", a[:, :, :K].double().cpu().numpy(), w.double().cpu().numpy())
+    assert np.abs(out[:, :, :N].double().cpu().numpy() - want).max() < 3e-2
+    assert out[:, :, N:].abs().max().item() == 0.0
+    assert not ops.head_gemm_mma_accepts(a[:, :, 1:K + 1], w, out[:, :, :N])      # rows that do not start on 16 bytes
+
+
 def test_the_scaled_rotation_tables():
     """All three ranges of wavelengths (kept, blended, divided) in one table, against the plain frequencies."""
     import torch
