@@ -162,6 +162,9 @@ GB_API int gb_gemm_tc5_ldw(const void* A, const void* W, void* C, int c_dtype, i
 GB_API int gb_gemm_tc5_grouped(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
                                int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
                                const int* row_map, cudaStream_t stream);
+GB_API int gb_gemm_tc5_grouped_act(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
+                                   int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
+                                   const int* row_map, float act_limit, float act_slope, cudaStream_t stream);
 GB_API int gb_gemm_tc5_pair_bias(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K, int64_t lda, int64_t ldc, int add,
                                  const float* bias, cudaStream_t stream);
 GB_API int gb_gemm_tc5_pair_add(const void* A, const void* W, void* C, int M, int N, int K, int64_t lda, int64_t ldc, cudaStream_t stream);

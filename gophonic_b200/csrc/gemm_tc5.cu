@@ -627,12 +627,21 @@ struct GroupWalk {
 
 template <typename TC>
 __device__ __forceinline__ void store_gated32(TC* __restrict__ dst, int left, bool vec_ok, const uint32_t (&g)[32], const uint32_t (&u)[32],
-                                              float f) {
+                                              float f, int kind, float limit, float slope) {
     float act[32];
+    if (kind == 2) {
+        // the clamped gate: y = c sigmoid(slope c) (v + 1), c = min(gate, limit), v = clamp(up, -limit, limit)
 #pragma unroll
-    for (int e = 0; e < 32; e++) {
-        const float a = f * __uint_as_float(g[e]), b = f * __uint_as_float(u[e]);
-        act[e] = __fdividef(a, 1.f + __expf(-a)) * b;
+        for (int e = 0; e < 32; e++) {
+            const float a = fminf(f * __uint_as_float(g[e]), limit), b = fminf(fmaxf(f * __uint_as_float(u[e]), -limit), limit);
+            act[e] = __fdividef(a, 1.f + __expf(-slope * a)) * (b + 1.f);
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+            const float a = f * __uint_as_float(g[e]), b = f * __uint_as_float(u[e]);
+            act[e] = __fdividef(a, 1.f + __expf(-a)) * b;
+        }
     }
     if (vec_ok && left >= 32) {
         if (sizeof(TC) == 2) {
@@ -667,7 +676,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_grouped_kernel(const __grid_
                                                                   const __grid_constant__ CUtensorMap map_w, TC* __restrict__ C,
                                                                   const int* __restrict__ offsets, int groups, int N, int K, int64_t ldc,
                                                                   int w_rows, int by_cols, int gated, const float* __restrict__ row_weight,
-                                                                  const int* __restrict__ row_map) {
+                                                                  const int* __restrict__ row_map, float act_limit, float act_slope) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
@@ -801,7 +810,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_grouped_kernel(const __grid_
                 if (gated) {
                     uint32_t u[32];
                     tmem_ld32(t_addr + (uint32_t)(BN / 2 + c0), u);
-                    if (mine) store_gated32<TC>(C + (int64_t)crow * ldc + n0 + c0, N - (n0 + c0), vec_ok, r, u, f);
+                    if (mine) store_gated32<TC>(C + (int64_t)crow * ldc + n0 + c0, N - (n0 + c0), vec_ok, r, u, f, gated, act_limit, act_slope);
                 } else {
                     store_cols32<TC>(C, ldc, crow, mine ? 0x7fffffff : 0, N, n0 + c0, r, 0, vec_ok);
                 }
@@ -821,7 +830,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc5_grouped_kernel(const __grid_
 
 template <typename TC>
 int launch_grouped(const void* A, const void* W, void* C, const int* offsets, int groups, int P, int N, int K, int64_t lda, int64_t ldw,
-                   int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight, const int* row_map, cudaStream_t stream) {
+                   int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight, const int* row_map, float act_limit, float act_slope,
+                   cudaStream_t stream) {
     const int smem = STAGES * STAGE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -847,7 +857,7 @@ int launch_grouped(const void* A, const void* W, void* C, const int* offsets, in
     const int64_t most = ((int64_t)ceil_div(P, BM) + (groups < P ? groups : P)) * ceil_div(N, tn);
     const int grid = most < sms ? (int)most : sms;
     cudaError_t e = launch_pdl(gemm_tc5_grouped_kernel<TC>, dim3(grid), dim3(THREADS), (size_t)smem, stream, map_a, map_w, (TC*)C, offsets,
-                               groups, N, K, ldc, w_rows, by_cols, gated, row_weight, row_map);
+                               groups, N, K, ldc, w_rows, by_cols, gated, row_weight, row_map, act_limit, act_slope);
     if (e != cudaSuccess) GB_REFUSE("gemm_tc5_grouped: launch failed: %s", cudaGetErrorString(e));
     return 0;
 }
@@ -919,9 +929,23 @@ GB_API int gb_gemm_tc5_swiglu(const void* A, const void* W, void* C, int c_dtype
 // offsets[e] .. offsets[e + 1] - 1 of A[P, K] (sorted by group; offsets[groups] <= P, on the device) times block e of W.
 // by_cols 0: block e is rows e * w_rows .. e * w_rows + N - 1 of W (gated: N gate rows, then N up rows; w_rows >= 2 N);
 // by_cols 1: block e is columns e * K .. e * K + K - 1 of W[N, groups * K].  C[row, 0 .. N - 1], or row row_map[row] of C.
+GB_API int gb_gemm_tc5_grouped_act(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
+                                   int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
+                                   const int* row_map, float act_limit, float act_slope, cudaStream_t stream);
+
 GB_API int gb_gemm_tc5_grouped(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
                                int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
                                const int* row_map, cudaStream_t stream) {
+    return gb_gemm_tc5_grouped_act(A, W, C, c_dtype, offsets, groups, P, N, K, lda, ldw, ldc, w_rows, by_cols, gated ? 1 : 0, row_weight, row_map, 0.f,
+                                   1.f, stream);
+}
+
+// The same with the gate's kind: gated 1: silu(f g) * (f u); gated 2: c sigmoid(slope c) (v + 1) with c = min(f g, limit) and
+// v = clamp(f u, -limit, limit).
+GB_API int gb_gemm_tc5_grouped_act(const void* A, const void* W, void* C, int c_dtype, const int* offsets, int groups, int P, int N, int K,
+                                   int64_t lda, int64_t ldw, int64_t ldc, int w_rows, int by_cols, int gated, const float* row_weight,
+                                   const int* row_map, float act_limit, float act_slope, cudaStream_t stream) {
+    if (gated < 0 || gated > 2) GB_REFUSE("gemm_tc5_grouped: unknown gate %d", gated);
     if (P <= 0 || N <= 0 || groups <= 0) return 0;
     if (K <= 0 || (K & 7)) GB_REFUSE("gemm_tc5_grouped: K = %d must be a positive multiple of 8", K);
     if ((lda & 7) || lda < K) GB_REFUSE("gemm_tc5_grouped: row stride %lld of A must be a multiple of 8 and at least K", (long long)lda);
@@ -933,10 +957,11 @@ GB_API int gb_gemm_tc5_grouped(const void* A, const void* W, void* C, int c_dtyp
     if (ldc < N) GB_REFUSE("gemm_tc5_grouped: row stride %lld of C is shorter than N = %d", (long long)ldc, N);
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) GB_REFUSE("gemm_tc5_grouped: operands must be 16-byte aligned");
     if (c_dtype == GB_F32)
-        return launch_grouped<float>(A, W, C, offsets, groups, P, N, K, lda, ldw, ldc, w_rows, by_cols, gated, row_weight, row_map, stream);
+        return launch_grouped<float>(A, W, C, offsets, groups, P, N, K, lda, ldw, ldc, w_rows, by_cols, gated, row_weight, row_map, act_limit, act_slope,
+                                     stream);
     if (c_dtype == GB_BF16)
         return launch_grouped<__nv_bfloat16>(A, W, C, offsets, groups, P, N, K, lda, ldw, ldc, w_rows, by_cols, gated, row_weight, row_map,
-                                             stream);
+                                             act_limit, act_slope, stream);
     GB_REFUSE("gemm_tc5_grouped: unknown output dtype %d", c_dtype);
 }
 

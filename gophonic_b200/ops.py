@@ -1443,11 +1443,13 @@ def gemm_grouped_fits(a_dtype, w: torch.Tensor, K: int, by_cols: bool) -> bool:
 
 
 def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, groups: int, *, by_cols: bool = False,
-                 gated: bool = False, row_weight: Optional[torch.Tensor] = None, row_map: Optional[torch.Tensor] = None) -> None:
+                 gated: bool = False, row_weight: Optional[torch.Tensor] = None, row_map: Optional[torch.Tensor] = None,
+                 gate: str = "swiglu", limit: float = 0.0, slope: float = 1.0) -> None:
     """One launch for the products of every group of rows: rows ``offsets[e] .. offsets[e + 1] - 1`` of ``a`` [P, K]
     (sorted by group; ``offsets`` int32 [groups + 1] on the device, never read on the host) times block e of ``w``.
     ``by_cols`` False: ``w`` is [groups * block, K] and block e its rows e * block ..; with ``gated`` a block is N gate
-    rows, then N up rows, and out = silu(f g) * (f u), f = ``row_weight[row]`` (1 if absent).  ``by_cols`` True: ``w`` is
+    rows, then N up rows, and out = silu(f g) * (f u), f = ``row_weight[row]`` (1 if absent), or with ``gate`` "glu_clamp"
+    c * sigmoid(slope * c) * (v + 1), c = min(f g, limit), v = clamp(f u, -limit, limit).  ``by_cols`` True: ``w`` is
     [N, groups * K] and block e its columns e * K ...  ``out`` is [*, N]; with ``row_map`` (int32 [P]) the result of
     row r is written to row ``row_map[r]`` of ``out``, otherwise to row r."""
     _need(a, "grouped gemm a", torch.bfloat16, 2, contiguous=False)
@@ -1476,9 +1478,12 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: t
         _need(row_map, "row map", torch.int32, 1)
         if row_map.numel() < P:
             raise KernelError(f"gemm_grouped: {row_map.numel()} mapped rows for {P}")
-    _check(_lib.gb_gemm_tc5_grouped(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), _ptr(offsets), c_int(groups), c_int(P), c_int(N), c_int(K),
-                                    c_int64(a.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(block), c_int(1 if by_cols else 0),
-                                    c_int(1 if gated else 0), _ptr(row_weight), _ptr(row_map), _stream()))
+    if gate not in ("swiglu", "glu_clamp"):
+        raise KernelError(f"gemm_grouped: unknown gate '{gate}'")
+    _check(_lib.gb_gemm_tc5_grouped_act(_ptr(a), _ptr(w), _ptr(out), _code(out.dtype), _ptr(offsets), c_int(groups), c_int(P), c_int(N), c_int(K),
+                                        c_int64(a.stride(0)), c_int64(w.stride(0)), c_int64(out.stride(0)), c_int(block), c_int(1 if by_cols else 0),
+                                        c_int(0 if not gated else (2 if gate == "glu_clamp" else 1)), _ptr(row_weight), _ptr(row_map),
+                                        c_float(limit), c_float(slope), _stream()))
 
 
 # ---- layers with the norm behind the sublayer, differential and latent attention ----------------

@@ -159,10 +159,10 @@ class MoE(FeedForward):
         per = self.up.shape[0] // s.experts     # rows of the stack an expert holds: ff, or gate and up
         one_launch = self._one_launch(x.dtype)
         bounds = None
-        if one_launch and self.act == "swiglu":
+        if one_launch and self.act != "relu2":
             # gate and up products, the pairs' weights and the activation in one kernel
             act = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
-            ops.gemm_grouped(xs, self.up, act, offsets, s.experts, gated=True, row_weight=sorted_w)
+            ops.gemm_grouped(xs, self.up, act, offsets, s.experts, gated=True, row_weight=sorted_w, gate=self.act, limit=self.limit, slope=self.slope)
         else:
             act = torch.empty((pairs, per), dtype=x.dtype, device=x.device)
             if one_launch:
