@@ -146,28 +146,38 @@ __global__ void __launch_bounds__(32 * WG * RG) attn_latent_mma_kernel(AttnParam
         // 16 keys: four 8 x 8 pieces (keys 0-7 and 8-15, channels 0-7 and 8-15); 8 keys: two pieces, addressed by lanes 0-15
         const bf16* kb = J == 2 ? kt + (warp * KW + (lane & 7) + (lane >> 4) * 8) * SD + ((lane >> 3) & 1) * 8
                                 : kt + (warp * KW + (lane & 7)) * SD + ((lane >> 3) & 1) * 8;
-        auto products = [&](float (&acc)[J][4], int step) {
-            uint32_t a[4];
+        // the operands of a step: a query fragment and the fragment(s) of this warp's keys
+        auto fetch = [&](uint32_t (&a)[4], uint32_t (&b)[4], int step) {
             ldmatrix_x4(a, qa + step * 16);
             if (J == 2) {
-                uint32_t b[4];
                 ldmatrix_x4(b, kb + step * 16);
-                mma_bf16_16816(acc[0], a[0], a[1], a[2], a[3], b[0], b[1]);
-                mma_bf16_16816(acc[J - 1], a[0], a[1], a[2], a[3], b[2], b[3]);
             } else {
-                uint32_t b[2];
-                ldmatrix_x2(b, kb + step * 16);
-                mma_bf16_16816(acc[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+                uint32_t b2[2];
+                ldmatrix_x2(b2, kb + step * 16);
+                b[0] = b2[0];
+                b[1] = b2[1];
             }
+        };
+        auto products = [&](float (&acc)[J][4], const uint32_t (&a)[4], const uint32_t (&b)[4]) {
+            mma_bf16_16816(acc[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+            if (J == 2) mma_bf16_16816(acc[J - 1], a[0], a[1], a[2], a[3], b[2], b[3]);
         };
         int ks = 0;
         for (; ks + 3 < KS; ks += 4) {
-            products(s, ks);
-            products(part[0], ks + 1);
-            products(part[1], ks + 2);
-            products(part[2], ks + 3);
+            // all eight fragments are asked for before the first product needs one
+            uint32_t a[4][4], b[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) fetch(a[u], b[u], ks + u);
+            products(s, a[0], b[0]);
+            products(part[0], a[1], b[1]);
+            products(part[1], a[2], b[2]);
+            products(part[2], a[3], b[3]);
         }
-        for (; ks < KS; ks++) products(s, ks);
+        for (; ks < KS; ks++) {
+            uint32_t a[4], b[4];
+            fetch(a, b, ks);
+            products(s, a, b);
+        }
 #pragma unroll
         for (int j = 0; j < J; j++)
 #pragma unroll
@@ -226,16 +236,29 @@ __global__ void __launch_bounds__(32 * WG * RG) attn_latent_mma_kernel(AttnParam
         }
         __syncthreads();
         // this warp's value columns over all 64 keys: the values are the first channels of the keys
+        {
+            // the value fragments are asked for one pair of column tiles ahead of the products that take them
+            const bf16* vb = kt + ((lane & 7) + ((lane >> 3) & 1) * 8) * SD + warp * (NT * 8) + (lane >> 4) * 8;
+            constexpr int PAIRS = NT / 2, STEPS = (LKT / 16) * PAIRS;
+            uint32_t pa[4], b[2][4];
+            ldmatrix_x4(pa, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * LPS + (lane >> 4) * 8);
+            ldmatrix_x4_trans(b[0], vb);
 #pragma unroll
-        for (int kk = 0; kk < LKT / 16; kk++) {
-            uint32_t pa[4];
-            ldmatrix_x4(pa, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * LPS + kk * 16 + (lane >> 4) * 8);
+            for (int st = 0; st < STEPS; st++) {
+                const int kk = st / PAIRS, c = st % PAIRS;
+                uint32_t pn[4];
+                if (st + 1 < STEPS) {
+                    const int kn = (st + 1) / PAIRS, cn = (st + 1) % PAIRS;
+                    ldmatrix_x4_trans(b[(st + 1) & 1], vb + kn * 16 * SD + cn * 16);
+                    if (cn == 0) ldmatrix_x4(pn, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * LPS + kn * 16 + (lane >> 4) * 8);
+                }
+                mma_bf16_16816(o[c * 2], pa[0], pa[1], pa[2], pa[3], b[st & 1][0], b[st & 1][1]);
+                mma_bf16_16816(o[c * 2 + 1], pa[0], pa[1], pa[2], pa[3], b[st & 1][2], b[st & 1][3]);
+                if (st + 1 < STEPS && (st + 1) % PAIRS == 0) {
 #pragma unroll
-            for (int c = 0; c < NT / 2; c++) {
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, kt + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * SD + warp * (NT * 8) + c * 16 + (lane >> 4) * 8);
-                mma_bf16_16816(o[c * 2], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
-                mma_bf16_16816(o[c * 2 + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
+                    for (int e = 0; e < 4; e++) pa[e] = pn[e];
+                }
+                (void)kk;
             }
         }
     }
